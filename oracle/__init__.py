@@ -1,0 +1,449 @@
+"""CPU oracle for the quantized-GEMM path.  TEST INFRASTRUCTURE ONLY.
+
+ctypes/numpy front end of ``b200q_oracle.c`` (the C restatement of the reference's
+CPU arithmetic) plus the seeded input generators for the benchmark configurations and
+the error metrics of the acceptance bar.  Only the tests, the smoke check and the
+bench's CPU-baseline leg import this package; the shipped library never does.
+
+Parity pins: decoders / packing / known answers against the constants in the
+reference's one-instruction tests, and the GEMM loop bit-for-bit against the compiled
+reference ``gemm_mma_cpu`` (``oracle/_ref/libcudaop_ref.so``) — see
+``tests/test_oracle_pins.py``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+import threading
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+_REF = None
+
+
+def build(force: bool = False) -> None:
+    """Compile liboracle.so (and oracle/_ref when the reference tree is mounted)."""
+    so = os.path.join(_HERE, "liboracle.so")
+    src = os.path.join(_HERE, "b200q_oracle.c")
+    if force or not os.path.exists(so) or os.path.getmtime(so) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "liboracle.so"])
+    if os.path.isdir("/root/reference/op/cpu") and (
+            force or not os.path.exists(os.path.join(_HERE, "_ref", "libcudaop_ref.so"))):
+        subprocess.check_call(["make", "-s", "-C", _HERE, "ref"])
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        build()
+        L = C.CDLL(os.path.join(_HERE, "liboracle.so"))
+        for name in ("oracle_decode_e2m1", "oracle_decode_ue4m3", "oracle_decode_e4m3",
+                     "oracle_decode_ue8m0"):
+            getattr(L, name).restype = C.c_float
+            getattr(L, name).argtypes = [C.c_uint8]
+        for name in ("oracle_decode_bf16", "oracle_decode_f16"):
+            getattr(L, name).restype = C.c_float
+            getattr(L, name).argtypes = [C.c_uint16]
+        for name in ("oracle_encode_e4m3", "oracle_encode_ue4m3", "oracle_encode_e2m1"):
+            getattr(L, name).restype = C.c_uint8
+            getattr(L, name).argtypes = [C.c_float]
+        for name in ("oracle_encode_bf16", "oracle_encode_f16"):
+            getattr(L, name).restype = C.c_uint16
+            getattr(L, name).argtypes = [C.c_float]
+        _LIB = L
+    return _LIB
+
+
+def ref_lib():
+    """The compiled reference gemm_mma_cpu, or None when it was never built."""
+    global _REF
+    if _REF is None:
+        p = os.path.join(_HERE, "_ref", "libcudaop_ref.so")
+        if not os.path.exists(p):
+            return None
+        _REF = C.CDLL(p)
+    return _REF
+
+
+def _p(a: np.ndarray):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _c(a, dt):
+    return np.ascontiguousarray(a, dtype=dt)
+
+
+# ----------------------------------------------------------------------- GEMM
+
+def gemm_f32(A: np.ndarray, B: np.ndarray, threads: int = 1, use_reference: bool = False) -> np.ndarray:
+    """C = A @ B.T with sequential fp32 accumulation (reference gemm_mma_cpu order).
+
+    ``threads`` > 1 calls the same function on disjoint row blocks (results are
+    identical: every output element is still one sequential sum).  With
+    ``use_reference`` the compiled reference object code does the work.
+    """
+    A = _c(A, np.float32); B = _c(B, np.float32)
+    M, K = A.shape; N, K2 = B.shape
+    assert K == K2
+    Cm = np.empty((M, N), np.float32)
+    if use_reference:
+        fn = ref_lib().cudaop_ref_gemm_mma_cpu
+    else:
+        fn = lib().oracle_gemm_f32
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+    threads = max(1, min(threads, M))
+    if threads == 1:
+        fn(_p(A), _p(B), _p(Cm), M, N, K)
+        return Cm
+    bounds = np.linspace(0, M, threads + 1).astype(int)
+
+    def work(lo, hi):
+        if hi > lo:
+            fn(_p(A[lo:hi]), _p(B), _p(Cm[lo:hi]), hi - lo, N, K)
+    ts = [threading.Thread(target=work, args=(bounds[i], bounds[i + 1])) for i in range(threads)]
+    [t.start() for t in ts]; [t.join() for t in ts]
+    return Cm
+
+
+def gemm_f64acc(A: np.ndarray, B: np.ndarray, threads: int = 1) -> np.ndarray:
+    A = _c(A, np.float32); B = _c(B, np.float32)
+    M, K = A.shape; N, _ = B.shape
+    Cm = np.empty((M, N), np.float64)
+    fn = lib().oracle_gemm_f64acc
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+    threads = max(1, min(threads, M))
+    bounds = np.linspace(0, M, threads + 1).astype(int)
+
+    def work(lo, hi):
+        if hi > lo:
+            fn(_p(A[lo:hi]), _p(B), _p(Cm[lo:hi]), hi - lo, N, K)
+    ts = [threading.Thread(target=work, args=(bounds[i], bounds[i + 1])) for i in range(threads)]
+    [t.start() for t in ts]; [t.join() for t in ts]
+    return Cm
+
+
+def gemm_f32_addc(A, B, C0):
+    A = _c(A, np.float32); B = _c(B, np.float32); C0 = _c(C0, np.float32)
+    M, K = A.shape; N, _ = B.shape
+    D = np.empty((M, N), np.float32)
+    fn = lib().oracle_gemm_f32_addc
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 4 + [C.c_int] * 3
+    fn(_p(A), _p(B), _p(C0), _p(D), M, N, K)
+    return D
+
+
+# --------------------------------------------------------------------- codecs
+
+def _lut(name, n=256):
+    f = getattr(lib(), name)
+    return np.array([f(i) for i in range(n)], np.float32)
+
+
+def decode_e4m3(q: np.ndarray) -> np.ndarray:
+    return _lut("oracle_decode_e4m3")[np.asarray(q, np.uint8)]
+
+
+def decode_ue4m3(q: np.ndarray) -> np.ndarray:
+    return _lut("oracle_decode_ue4m3")[np.asarray(q, np.uint8)]
+
+
+def decode_e2m1(nib: np.ndarray) -> np.ndarray:
+    return _lut("oracle_decode_e2m1", 16)[np.asarray(nib, np.uint8) & 0xF]
+
+
+def encode_e4m3(x: np.ndarray, scale: float = 1.0) -> np.ndarray:
+    x = _c(x, np.float32)
+    out = np.empty(x.shape, np.uint8)
+    fn = lib().oracle_encode_e4m3_n
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_float]
+    fn(_p(x), _p(out), x.size, float(scale))
+    return out
+
+
+def decode_bf16(h: np.ndarray) -> np.ndarray:
+    return (np.asarray(h, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def encode_bf16(x: np.ndarray) -> np.ndarray:
+    x = _c(x, np.float32)
+    out = np.empty(x.shape, np.uint16)
+    fn = lib().oracle_encode_bf16_n
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    fn(_p(x), _p(out), x.size)
+    return out
+
+
+def encode_f16(x):
+    return np.asarray(x, np.float32).astype(np.float16).view(np.uint16)
+
+
+def decode_f16(h):
+    return np.asarray(h, np.uint16).view(np.float16).astype(np.float32)
+
+
+def pack_s4(v: np.ndarray) -> np.ndarray:
+    """int8 values in [-8,7], last axis even -> bytes, low nibble = lower K index."""
+    v = _c(v, np.int8)
+    out = np.empty(v.shape[:-1] + (v.shape[-1] // 2,), np.uint8)
+    fn = lib().oracle_pack_s4
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    fn(_p(v), _p(out), v.size)
+    return out
+
+
+def unpack_s4(b: np.ndarray) -> np.ndarray:
+    b = _c(b, np.uint8)
+    out = np.empty(b.shape[:-1] + (b.shape[-1] * 2,), np.int8)
+    fn = lib().oracle_unpack_s4
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    fn(_p(b), _p(out), out.size)
+    return out
+
+
+def pack_u4(v):
+    v = _c(v, np.uint8)
+    out = np.empty(v.shape[:-1] + (v.shape[-1] // 2,), np.uint8)
+    fn = lib().oracle_pack_u4
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    fn(_p(v), _p(out), v.size)
+    return out
+
+
+def unpack_u4(b):
+    b = _c(b, np.uint8)
+    out = np.empty(b.shape[:-1] + (b.shape[-1] * 2,), np.uint8)
+    fn = lib().oracle_unpack_u4
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    fn(_p(b), _p(out), out.size)
+    return out
+
+
+def sp24_compress(dense_u8: np.ndarray):
+    """dense[M,K] bytes (2 of every 4 non-zero) -> (comp[M,K/2], meta[M,K/8])."""
+    d = _c(dense_u8, np.uint8)
+    M, K = d.shape
+    comp = np.zeros((M, K // 2), np.uint8)
+    meta = np.zeros((M, K // 8), np.uint8)
+    fn = lib().oracle_sp24_compress_u8
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p] * 3 + [C.c_int] * 2
+    if fn(_p(d), _p(comp), _p(meta), M, K) != 0:
+        raise ValueError("a group of four holds more than two non-zeros")
+    return comp, meta
+
+
+def sp24_expand(comp, meta):
+    comp = _c(comp, np.uint8); meta = _c(meta, np.uint8)
+    M, K2 = comp.shape
+    dense = np.empty((M, K2 * 2), np.uint8)
+    fn = lib().oracle_sp24_expand_u8
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_void_p] * 3 + [C.c_int] * 2
+    if fn(_p(comp), _p(meta), _p(dense), M, K2 * 2) != 0:
+        raise ValueError("metadata nibble is not an ascending pair")
+    return dense
+
+
+def quant_rows_e4m3(x: np.ndarray):
+    x = _c(x, np.float32)
+    R, Cc = x.shape
+    q = np.empty((R, Cc), np.uint8); s = np.empty(R, np.float32)
+    fn = lib().oracle_quant_rows_e4m3
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 3 + [C.c_int] * 2
+    fn(_p(x), _p(q), _p(s), R, Cc)
+    return q, s
+
+
+def quant_nvfp4(x: np.ndarray, g: float):
+    x = _c(x, np.float32)
+    R, Cc = x.shape
+    q = np.empty((R, Cc // 2), np.uint8); sf = np.empty((R, Cc // 16), np.uint8)
+    fn = lib().oracle_quant_nvfp4
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 3 + [C.c_int] * 2 + [C.c_float]
+    fn(_p(x), _p(q), _p(sf), R, Cc, float(g))
+    return q, sf
+
+
+def dequant_nvfp4(q, sf, g: float) -> np.ndarray:
+    q = _c(q, np.uint8); sf = _c(sf, np.uint8)
+    R, C2 = q.shape
+    out = np.empty((R, C2 * 2), np.float32)
+    fn = lib().oracle_dequant_nvfp4
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 3 + [C.c_int] * 2 + [C.c_float]
+    fn(_p(q), _p(sf), _p(out), R, C2 * 2, float(g))
+    return out
+
+
+def dequant_w4(wq, s_f16, group: int = 128) -> np.ndarray:
+    wq = _c(wq, np.uint8); s = _c(s_f16, np.uint16)
+    N, K2 = wq.shape
+    out = np.empty((N, K2 * 2), np.float32)
+    fn = lib().oracle_dequant_w4
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 3 + [C.c_int] * 3
+    fn(_p(wq), _p(s), _p(out), N, K2 * 2, group)
+    return out
+
+
+def swiglu(g, u):
+    g = _c(g, np.float32); u = _c(u, np.float32)
+    h = np.empty_like(g)
+    fn = lib().oracle_swiglu
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 3 + [C.c_size_t]
+    fn(_p(g), _p(u), _p(h), g.size)
+    return h
+
+
+def shard_cols(w: np.ndarray, rank: int, world: int) -> np.ndarray:
+    w = np.ascontiguousarray(w)
+    rows, cols = w.shape
+    out = np.empty((rows, cols // world), w.dtype)
+    fn = lib().oracle_shard_cols
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_int]
+    fn(_p(w), _p(out), rows, cols, w.itemsize, rank, world)
+    return out
+
+
+def shard_rows(w: np.ndarray, rank: int, world: int) -> np.ndarray:
+    w = np.ascontiguousarray(w)
+    rows, cols = w.shape
+    out = np.empty((rows // world, cols), w.dtype)
+    fn = lib().oracle_shard_rows
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_int, C.c_int]
+    fn(_p(w), _p(out), rows, cols, w.itemsize, rank, world)
+    return out
+
+
+def compare(actual, expected):
+    """(max_abs, max_rel) with the reference's 1e-6 denominator floor."""
+    a = _c(actual, np.float32).ravel(); e = _c(expected, np.float32).ravel()
+    ma = C.c_float(); mr = C.c_float()
+    fn = lib().oracle_compare
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
+    fn(_p(a), _p(e), a.size, C.byref(ma), C.byref(mr))
+    return ma.value, mr.value
+
+
+# ------------------------------------------------------------ acceptance bar
+
+def bf16_ulp(ref: np.ndarray) -> np.ndarray:
+    """Spacing of bf16 numbers at |ref| (8 significant bits; subnormal floor 2^-133)."""
+    a = np.abs(np.asarray(ref, np.float64))
+    e = np.floor(np.log2(np.maximum(a, 2.0 ** -126)))
+    return np.exp2(e - 7)
+
+
+def error_report(out_bf16_as_f32: np.ndarray, ref_f32: np.ndarray, ref_f64=None, k_dim: int | None = None) -> dict:
+    """Relative Frobenius error and the bf16-ulp criterion against the fp32 oracle.
+
+    The bar: rel-Frobenius <= 1e-3 and |out - ref| <= 2 ulp_bf16(ref) elementwise.  An
+    output that sits where the dot product cancels to nearly zero can miss the ulp
+    bound for a perfect kernel (its ulp is far below the fp32 summation noise), so
+    the report also counts violators and gives ``max_ulp_floor``: the same criterion
+    with the error allowed an absolute floor of ``noise`` = 4 * eps_f32 * sqrt(K) *
+    rms(ref) — the order of the oracle's own sequential-sum rounding error.
+    """
+    o = np.asarray(out_bf16_as_f32, np.float64); r = np.asarray(ref_f32, np.float64)
+    diff = np.abs(o - r)
+    fro = float(np.linalg.norm(o - r) / max(np.linalg.norm(r), 1e-30))
+    ulp = bf16_ulp(r)
+    ulps = diff / ulp
+    rms = float(np.sqrt(np.mean(r * r))) if r.size else 0.0
+    noise = 4.0 * 2.0 ** -24 * np.sqrt(float(k_dim or 1)) * rms
+    ulps_floor = np.maximum(diff - noise, 0.0) / ulp
+    rep = {
+        "rel_fro": fro,
+        "max_ulp": float(ulps.max()) if r.size else 0.0,
+        "violators_2ulp": int((ulps > 2.0).sum()),
+        "violators_max_abs_ref": float(np.abs(r[ulps > 2.0]).max()) if (ulps > 2.0).any() else 0.0,
+        "max_ulp_floor": float(ulps_floor.max()) if r.size else 0.0,
+        "noise_floor": noise, "rms_ref": rms,
+    }
+    if ref_f64 is not None:
+        r64 = np.asarray(ref_f64, np.float64)
+        rep["max_ulp_vs_f64"] = float((np.abs(o - r64) / bf16_ulp(r64)).max())
+    return rep
+
+
+# ------------------------------------------------------ seeded input makers
+# Shapes and distributions as the benchmark configurations state them; the
+# generator is numpy's PCG64 seeded per call (seed 0 unless stated).
+
+def make_fp8_case(M, N, K, seed=0):
+    """A[M,K], B[N,K] ~ N(0,1), one fp32 per-tensor scale each: s = max|x|/448."""
+    rng = np.random.default_rng(seed)
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    B = rng.standard_normal((N, K), dtype=np.float32)
+    sa = np.float32(np.abs(A).max() / 448.0); sb = np.float32(np.abs(B).max() / 448.0)
+    return encode_e4m3(A, sa), encode_e4m3(B, sb), float(sa), float(sb)
+
+
+def make_w4a16_case(M, N, K, group=128, seed=0):
+    rng = np.random.default_rng(seed)
+    wq = rng.integers(-8, 8, size=(N, K), dtype=np.int8)
+    s = rng.uniform(0.005, 0.02, size=(N, K // group)).astype(np.float32)
+    x = rng.standard_normal((M, K), dtype=np.float32)
+    return encode_bf16(x), pack_s4(wq), encode_f16(s)
+
+
+def make_nvfp4_operand(R, K, rng):
+    x = rng.standard_normal((R, K), dtype=np.float32)
+    g = np.float32(np.abs(x).max() / (6.0 * 448.0))
+    q, sf = quant_nvfp4(x, g)
+    return q, sf, float(g)
+
+
+def make_nvfp4_case(M, N, K, seed=0):
+    rng = np.random.default_rng(seed)
+    aq, sfa, ga = make_nvfp4_operand(M, K, rng)
+    bq, sfb, gb = make_nvfp4_operand(N, K, rng)
+    return aq, sfa, ga, bq, sfb, gb
+
+
+def make_sparse_fp8_case(M, N, K, seed=0):
+    """Sparse A: in every 4 consecutive K two positions chosen uniformly, N(0,1) values."""
+    rng = np.random.default_rng(seed)
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    pairs = np.array([[0, 1], [0, 2], [1, 2], [0, 3], [1, 3], [2, 3]])
+    pick = pairs[rng.integers(0, 6, size=(M, K // 4))]
+    mask = np.zeros((M, K // 4, 4), bool)
+    np.put_along_axis(mask, pick, True, axis=2)
+    A = np.where(mask.reshape(M, K), A, np.float32(0))
+    B = rng.standard_normal((N, K), dtype=np.float32)
+    sa = np.float32(np.abs(A).max() / 448.0); sb = np.float32(np.abs(B).max() / 448.0)
+    Aq = encode_e4m3(A, sa)
+    # a retained value may quantise to zero: still a legal 2:4 row (<= 2 non-zeros)
+    comp, meta = sp24_compress(Aq)
+    return comp, meta, encode_e4m3(B, sb), float(sa), float(sb)
+
+
+def make_mlp_case(tokens, hidden, inter, seed=0):
+    """X bf16 N(0,1); W_gate/W_up [inter, hidden], W_down [hidden, inter] as E4M3 of
+    N(0,1) draws with per-output-channel fp32 scales ~ U(0.001, 0.01)."""
+    rng = np.random.default_rng(seed)
+    x = encode_bf16(rng.standard_normal((tokens, hidden), dtype=np.float32))
+
+    def w(rows, cols):
+        return encode_e4m3(rng.standard_normal((rows, cols), dtype=np.float32), 1.0), \
+            rng.uniform(0.001, 0.01, size=rows).astype(np.float32)
+    wg, sg = w(inter, hidden); wu, su = w(inter, hidden); wd, sd = w(hidden, inter)
+    return x, wg, sg, wu, su, wd, sd
