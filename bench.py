@@ -1,0 +1,389 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-GEMM path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one forward pass of the tensor-parallel SwiGLU MLP of the benchmark
+configuration (tokens 4096, hidden 8192, intermediate 28672, E4M3 weights with per-channel
+scales, bf16 activations), sharded over N ranks (gate/up column-parallel, down row-parallel,
+one sum all-reduce).  Total work is fixed as N grows ("strong" scaling).  Rank 0 prints ONE JSON
+line; at N=1 it also carries the per-format GEMM cases (FP8 8192^3, W4A16 decode, ...) with
+their roofline fractions, and the reference's CPU GEMM path timed on the host cores.
+
+``--impl reference`` times the reference project's own CPU implementation of the same path
+(its compiled gemm_mma_cpu from oracle/_ref when present, else the C restatement in oracle/)
+on a bounded sample of the same workload, all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+TOKENS, HIDDEN, INTER = 4096, 8192, 28672
+MLP_FLOPS = 2 * TOKENS * HIDDEN * (2 * INTER) + 2 * TOKENS * INTER * HIDDEN
+NOMINAL = {"fp8_tflops": 4500.0, "fp4_tflops": 9000.0, "hbm_gbs": 7700.0}
+
+
+def measured_peaks() -> dict:
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p)); d["source"] = "measured"
+        return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ------------------------------------------------------------------------- clocks
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True); self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, mx, reasons, pw = [], [], set(), []
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2])); pw.append(float(r[3]))
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            except Exception:
+                continue
+        hi = [s for s, p in zip(sm, pw) if p >= 0.5 * max(pw)] if pw else sm
+        return {"sm_mhz": statistics.median(hi) if hi else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ CPU reference arm
+
+def cpu_mlp_sample(n_tokens: int, weights_host, x_host, threads: int, use_ref: bool):
+    """The whole MLP for ``n_tokens`` tokens on the host, every GEMM by the reference's CPU loop."""
+    import numpy as np
+    import oracle
+    wg, sg, wu, su, wd, sd = weights_host
+    x = oracle.decode_bf16(x_host[:n_tokens])
+    t0 = time.perf_counter()
+    xq, sx = oracle.quant_rows_e4m3(x)
+    X = oracle.decode_e4m3(xq)
+    g = oracle.gemm_f32(X, wg, threads=threads, use_reference=use_ref) * (sx[:, None] * sg[None, :])
+    u = oracle.gemm_f32(X, wu, threads=threads, use_reference=use_ref) * (sx[:, None] * su[None, :])
+    h = oracle.decode_bf16(oracle.encode_bf16(oracle.swiglu(g, u)))
+    hq, sh = oracle.quant_rows_e4m3(h)
+    y = oracle.gemm_f32(oracle.decode_e4m3(hq), wd, threads=threads, use_reference=use_ref) * (sh[:, None] * sd[None, :])
+    dt = time.perf_counter() - t0
+    return dt, oracle.encode_bf16(y)
+
+
+def host_weights(seed: int = 0):
+    """E4M3 weights N(0,1) with per-output-channel scales U(0.001, 0.01), decoded to fp32 for the CPU arm."""
+    import numpy as np
+    import oracle
+    rng = np.random.default_rng(seed)
+
+    def w(rows, cols):
+        q = oracle.encode_e4m3(rng.standard_normal((rows, cols), dtype=np.float32))
+        return oracle.decode_e4m3(q), rng.uniform(0.001, 0.01, rows).astype(np.float32)
+    wg, sg = w(INTER, HIDDEN); wu, su = w(INTER, HIDDEN); wd, sd = w(HIDDEN, INTER)
+    return wg, sg, wu, su, wd, sd
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import numpy as np
+    import oracle
+    oracle.build()
+    use_ref = oracle.ref_lib() is not None
+    cores = os.cpu_count() or 1
+    weights = host_weights()
+    rng = np.random.default_rng(1)
+    sample = args.cpu_tokens
+    x = oracle.encode_bf16(rng.standard_normal((sample, HIDDEN), dtype=np.float32))
+    times = []
+    for i in range(args.warmup + args.steps):
+        dt, _ = cpu_mlp_sample(sample, weights, x, cores, use_ref)
+        if i >= args.warmup:
+            times.append(dt)
+    t = sum(times) / len(times)
+    val = sample / t
+    desc = {"value": val, "unit": "tokens/s", "cores": cores, "kind": "reference" if use_ref else "port",
+            "sample": f"{sample} of {TOKENS} tokens through the whole MLP per step (all GEMMs by gemm_mma_cpu on "
+                      f"row blocks, one thread per core); GFLOP/s = {MLP_FLOPS / TOKENS * sample / t / 1e9:.2f}"}
+    print(json.dumps({
+        "impl": "reference", "metric": "tp_mlp_tokens_per_s", "value": val, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32",
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "cpu_baseline": desc,
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(n):
+    return {"workload": f"SwiGLU TP-MLP tokens={TOKENS} hidden={HIDDEN} intermediate={INTER}, E4M3 weights + "
+                        f"per-channel fp32 scales, bf16 activations, tp{n}",
+            "tokens": TOKENS, "hidden": HIDDEN, "intermediate": INTER, "parallelism": f"tp{n}",
+            "l2": "per-rank weights + activations exceed the 126 MB L2 every step"}
+
+
+# ------------------------------------------------------------------------- GPU arm
+
+def time_graph(fn, iters: int, reps: int = 5):
+    """Captures ``iters`` calls of fn() into one CUDA graph and returns the best ms per call."""
+    import torch
+    fn(); torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(iters):
+            fn(i)
+    g.replay(); torch.cuda.synchronize()
+    best = 1e30
+    for _ in range(reps):
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(); g.replay(); e1.record(); torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) / iters)
+    return best
+
+
+def time_loop(fn, iters: int, warm: int = 3):
+    import torch
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record(); torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def gemm_cases(peaks):
+    """Per-format GEMM numbers (rank 0, N=1): TFLOPS or GB/s and fractions of nominal / measured peaks."""
+    import torch
+    import cudaop_b200 as ops
+    L = ops.lib()
+    out = {}
+    st = lambda: torch.cuda.current_stream().cuda_stream
+    fp8_meas = 2.0 * peaks["bf16_tflops"]
+    # FP8 8192^3 (operands 128 MB > L2 is not true here: 2 x 64 MB + 128 MB C; C alone exceeds L2)
+    S = 8192
+    a = torch.randint(0, 120, (S, S), dtype=torch.uint8, device="cuda")
+    b = torch.randint(0, 120, (S, S), dtype=torch.uint8, device="cuda")
+    c = torch.empty((S, S), dtype=torch.bfloat16, device="cuda")
+    ms = time_loop(lambda: L.b200q_gemm_fp8(a.data_ptr(), b.data_ptr(), c.data_ptr(), S, S, S, 1.0, 1.0, st()), 20)
+    tf = 2 * S ** 3 / ms / 1e9
+    out["fp8_8192"] = {"ms": ms, "tflops": tf, "frac_nominal_4500": tf / NOMINAL["fp8_tflops"],
+                       "frac_2x_measured_bf16": tf / fp8_meas}
+    del a, b, c
+    # W4A16 decode: 80 distinct weight sets (671 MB > L2) cycled inside one CUDA graph
+    N = K = 4096
+    nsets = 80
+    wq = torch.randint(0, 256, (nsets, N, K // 2), dtype=torch.uint8, device="cuda")
+    sc = (torch.rand((nsets, N, K // 128), device="cuda") * 0.015 + 0.005).to(torch.float16)
+    for M in (1, 16):
+        x = torch.randn((M, K), device="cuda").to(torch.bfloat16)
+        y = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+
+        def call(i=0):
+            j = i % nsets
+            L.b200q_gemm_w4a16(x.data_ptr(), wq[j].data_ptr(), sc[j].data_ptr(), y.data_ptr(), M, N, K, 128, st())
+        ms = time_graph(call, 2 * nsets)
+        byts = N * K // 2 + N * (K // 128) * 2 + 2 * M * K + 2 * M * N
+        gbs = byts / ms / 1e6
+        out[f"w4a16_m{M}"] = {"us": ms * 1e3, "gbs": gbs, "frac_measured_hbm": gbs / peaks["hbm_gbs"],
+                              "frac_nominal_7700": gbs / NOMINAL["hbm_gbs"], "bytes": byts,
+                              "note": "80 distinct weight sets cycled in one CUDA graph"}
+    del wq, sc
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    import cudaop_b200 as ops
+    from cudaop_b200.mlp import TensorParallelMLP
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    if world != args.gpus and rank == 0:
+        print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
+    ops.lib()   # fails loudly if the CUDA library is missing
+    peaks = measured_peaks()
+
+    # synthetic weights, generated shard by shard on the device from per-row seeds so that every
+    # world size multiplies the same matrices
+    loc = INTER // world
+    gen = torch.Generator(device=dev)
+
+    def rand_e4m3(rows, cols, seed):
+        gen.manual_seed(seed)
+        return torch.randn((rows, cols), device=dev, generator=gen).to(torch.float8_e4m3fn).view(torch.uint8)
+
+    def rand_scale(n, seed):
+        gen.manual_seed(seed)
+        return torch.rand((n,), device=dev, generator=gen) * 0.009 + 0.001
+    # shard r of gate/up = block r of `world` equal row blocks; generate only this rank's block
+    wg = rand_e4m3(loc, HIDDEN, 1000 + rank) ; wu = rand_e4m3(loc, HIDDEN, 2000 + rank)
+    wd = rand_e4m3(HIDDEN, loc, 3000 + rank)
+    sg = rand_scale(loc, 4000 + rank); su = rand_scale(loc, 5000 + rank); sd = rand_scale(HIDDEN, 6000)
+    mlp = TensorParallelMLP(wg, sg, wu, su, wd, sd, rank=rank, world=world, device=dev, max_tokens=TOKENS,
+                            chunks=args.chunks if world > 1 else 1, presharded=True)
+    del wg, wu, wd
+
+    gen.manual_seed(7)
+    x_host = torch.randn((TOKENS, HIDDEN), generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).pin_memory()
+    y_host = torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16).pin_memory()
+    x = x_host.to(dev, non_blocking=True)
+    y = torch.empty((TOKENS, HIDDEN), dtype=torch.bfloat16, device=dev)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        sync_all()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        sync_all()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    # ---- device-resident steps (the headline `value`) with events around the top kernel
+    mlp.top_kernel_events = []
+    ms_step = timed(lambda: mlp.forward(x, out=y), args.steps, args.warmup)
+    evs = mlp.top_kernel_events; mlp.top_kernel_events = None
+    torch.cuda.synchronize()
+    top_ms = [a.elapsed_time(b) for a, b in evs[-args.steps * max(1, mlp.chunks if world > 1 else 1):]]
+    launches = mlp.kernel_launches_per_forward * args.steps
+    # ---- end to end: pinned host input -> device, forward, result back to pinned host memory
+    def e2e_step():
+        x.copy_(x_host, non_blocking=True)
+        mlp.forward(x, out=y)
+        y_host.copy_(y, non_blocking=True)
+    ms_e2e = timed(e2e_step, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    assert ops.status() == 0, "a kernel gave up on a bounded wait"
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier(); dist.destroy_process_group()
+        return
+
+    top_avg = sum(top_ms) / max(1, len(top_ms))
+    chunks = mlp.chunks if world > 1 else 1
+    top_flops = 2 * (TOKENS // chunks) * HIDDEN * (2 * loc)
+    top_tf = top_flops / top_avg / 1e9 if top_avg > 0 else 0.0
+    peak = 2.0 * peaks["bf16_tflops_sustained"]
+    line = {
+        "metric": "tp_mlp_tokens_per_s", "value": TOKENS / (ms_step * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 acc -> bf16",
+        "data": "synthetic", "config": workload_config(world),
+        "tflops": MLP_FLOPS / (ms_step * 1e-3) / 1e12,
+        "clocks": clocks,
+        "e2e": {"value": TOKENS / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": TOKENS * HIDDEN * 2, "d2h_bytes_per_step": TOKENS * HIDDEN * 2},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "kernel": "gemm_fp8_kernel<SwiGLU> (gate/up projection)",
+                     "achieved": top_tf, "peak": peak, "unit": "TFLOP/s", "frac": top_tf / peak,
+                     "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} (FP8 runs at twice the bf16 "
+                                    "rate on the same tensor pipe; no FP8 figure is measured by the driver)",
+                     "frac_nominal_4500": top_tf / NOMINAL["fp8_tflops"], "launch_ms": top_avg,
+                     "flops_per_launch": top_flops, "traffic": None},
+    }
+    if world == 1 and not args.no_cases:
+        line["cases"] = gemm_cases(peaks)
+    if world == 1 and not args.no_cpu:
+        import oracle
+        oracle.build()
+        use_ref = oracle.ref_lib() is not None
+        cores = os.cpu_count() or 1
+        weights = host_weights()
+        import numpy as np
+        xs = x_host[:args.cpu_tokens].view(torch.int16).numpy().view(np.uint16)
+        dt, _ = cpu_mlp_sample(args.cpu_tokens, weights, xs, cores, use_ref)
+        line["cpu_baseline"] = {"value": args.cpu_tokens / dt, "unit": "tokens/s", "cores": cores,
+                                "kind": "reference" if use_ref else "port",
+                                "sample": f"{args.cpu_tokens} of {TOKENS} tokens through the whole MLP, "
+                                          f"{dt:.1f} s, {MLP_FLOPS / TOKENS * args.cpu_tokens / dt / 1e9:.2f} GFLOP/s"}
+    print(json.dumps(line))
+    if world > 1:
+        dist.barrier(); dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--chunks", type=int, default=4, help="token chunks for all-reduce overlap (N > 1)")
+    ap.add_argument("--cpu-tokens", type=int, default=64, help="tokens in the CPU-baseline sample")
+    ap.add_argument("--no-cases", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,400 @@
+// Inline-PTX wrappers for sm_100a: mbarrier, TMA (non-multicast), tcgen05 (TMEM
+// allocation, UMMA issue/commit, TMEM loads) and the bounded-wait helper.
+//
+// Convention (as in the reference's op/ptx_utils.cuh, AGENTS.md:23-26): all PTX of
+// the library lives here, one wrapper per instruction, each stating the instruction
+// it emits.  Every wait is bounded: a wait that runs out records where it gave up in
+// a status word and returns false; it never traps and never spins forever.
+#pragma once
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace ptx {
+
+// Status word layout written on a timed-out wait: bit 31 set, bits [30:24] = site
+// id, bits [23:0] = block index (saturated).
+constexpr uint32_t kStatusTimeout = 0x80000000u;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p)
+{
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ unsigned long long globaltimer_ns()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ uint32_t lane_id()
+{
+    uint32_t l;
+    asm volatile("mov.u32 %0, %laneid;" : "=r"(l));
+    return l;
+}
+
+// elect.sync: one lane of the (converged) warp returns true.
+__device__ __forceinline__ bool elect_one()
+{
+    uint32_t pred;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(pred));
+    return pred != 0;
+}
+
+// ---------------------------------------------------------------- mbarrier
+
+// mbarrier.init.shared::cta.b64
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+// fence.mbarrier_init.release.cluster: makes the inits visible to the async proxy / cluster
+__device__ __forceinline__ void fence_mbar_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// mbarrier.arrive.expect_tx.shared::cta.b64: one arrival + expected transaction bytes
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// mbarrier.arrive.shared::cta.b64
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// mbarrier.arrive.release.cluster.shared::cluster.b64 on a barrier of any CTA in the cluster
+// (address produced by mapa).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// mbarrier.try_wait.parity.shared::cta.b64
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait on a phase parity.  Returns false after kWaitLimitNs, having recorded
+// (site, block) in *status.  The caller must then leave its loop and fall through to
+// the kernel's tear-down.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* status, uint32_t site)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        if ((++spins & 0xFFu) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+            uint32_t b = blockIdx.x > 0xFFFFFFu ? 0xFFFFFFu : blockIdx.x;
+            atomicCAS(status, 0u, kStatusTimeout | (site << 24) | b);
+            return false;
+        }
+    }
+    return true;
+}
+
+// ------------------------------------------------------------------- fences
+
+// fence.proxy.async.shared::cta: generic-proxy smem writes -> visible to the async proxy (TMA/UMMA)
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before_sync()
+{
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after_sync()
+{
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------- TMA
+
+// prefetch.tensormap: pulls the descriptor (a __grid_constant__ kernel parameter) into cache
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tm)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tm)) : "memory");
+}
+
+// cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes (no multicast)
+// x = innermost coordinate; x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* tm, uint32_t bar, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// cp.async.bulk.tensor.2d.global.shared::cta.bulk_group (store; coordinates must be >= 0)
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t smem_src, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+        ::"l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_src), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tma_store_commit()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// wait until at most N bulk groups still read their shared-memory source
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tma_store_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// -------------------------------------------------------------------- TMEM
+
+// tcgen05.alloc.cta_group::1: whole-warp, writes the TMEM base address to smem
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_2cta(uint32_t smem_result, uint32_t ncols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_2cta()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2cta(uint32_t taddr, uint32_t ncols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// ------------------------------------------------------------- descriptors
+
+// Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128
+// bytes with the 128-byte swizzle (what a SWIZZLE_128B TMA box of 128 bytes x rows
+// writes): 8-row groups are 1024 bytes apart (stride byte offset), the leading byte
+// offset is unused for swizzled K-major (encoded 1), descriptor version 1 (sm_100),
+// layout type 2 = SWIZZLE_128B.  The tile base must be 1024-byte aligned; advancing
+// along K inside the swizzle row adds the byte offset (>>4) to the start field.
+__device__ __forceinline__ uint64_t smem_desc_sw128_kmajor(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);   // start address, bits [0,14)
+    d |= static_cast<uint64_t>(1) << 16;                        // leading byte offset (16 B units)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;                // stride byte offset (16 B units)
+    d |= static_cast<uint64_t>(1) << 46;                        // descriptor version
+    d |= static_cast<uint64_t>(2) << 61;                        // SWIZZLE_128B
+    return d;
+}
+
+// Same, for an un-swizzled K-major tile made of 8-row x 16-byte core matrices:
+// lbo = byte distance between core matrices adjacent in K, sbo = between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc_noswizzle_kmajor(uint32_t smem_addr, uint32_t lbo, uint32_t sbo)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>((lbo >> 4) & 0x3FFFu) << 16;
+    d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;
+}
+
+// Instruction descriptor, kind::f8f6f4 / kind::f16 (dense): fp32 accumulate, both
+// operands K-major.  Formats for f8f6f4: 0 = E4M3, 1 = E5M2, 5 = E2M1.
+__host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n,
+                                                  bool sparse = false)
+{
+    return (sparse ? (1u << 2) : 0u) | (1u << 4) /* D = f32 */ | (a_fmt << 7) | (b_fmt << 10) |
+           ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+// Instruction descriptor for block-scaled kinds (mxf8f6f4 / mxf4nvf4): no D-format
+// field (always f32); scale-factor ids select a byte column inside the 32-bit TMEM
+// scale column; scale format 0 = UE4M3, 1 = UE8M0.
+__host__ __device__ constexpr uint32_t umma_idesc_block_scaled(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n,
+                                                               uint32_t a_sf_id, uint32_t b_sf_id, uint32_t sf_fmt)
+{
+    return (b_sf_id << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | (sf_fmt << 23) |
+           ((m >> 4) << 24) | (a_sf_id << 29);
+}
+
+// -------------------------------------------------------------------- UMMA
+
+// tcgen05.mma.cta_group::1.kind::f8f6f4  D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void umma_f8f6f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// tcgen05.mma.cta_group::2.kind::f8f6f4 (issued by the leader CTA of a pair)
+__device__ __forceinline__ void umma_f8f6f4_2cta(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// tcgen05.mma.cta_group::1.kind::f16 (bf16 / fp16 operands)
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X: E2M1 operands with one
+// UE4M3 scale per 16 K-elements, scales read from TMEM.
+__device__ __forceinline__ void umma_mxf4nvf4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+
+// tcgen05.mma.sp.cta_group::1.kind::f8f6f4: A is 2:4-compressed, metadata read from TMEM.
+__device__ __forceinline__ void umma_sp_f8f6f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t meta_tmem, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.sp.cta_group::1.kind::f8f6f4 [%0], %1, %2, [%5], %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(meta_tmem)
+        : "memory");
+}
+
+// tcgen05.commit: the mbarrier receives one arrival when every tcgen05 async operation issued
+// so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// cta_group::2 form; cta_mask selects which CTAs of the pair get the arrival (signal multicast, not
+// a data load).
+__device__ __forceinline__ void umma_commit_2cta(uint32_t bar, uint16_t cta_mask)
+{
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(cta_mask)
+        : "memory");
+}
+
+// tcgen05.cp.cta_group::1.32x128b.warpx4: copies 32 rows x 16 bytes from smem (described by a
+// no-swizzle descriptor) into 32 TMEM lanes x 4 columns, replicated to all four lane quadrants.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t smem_desc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// tcgen05.cp.cta_group::1.128x128b: 128 rows x 16 bytes -> 128 lanes x 4 columns
+__device__ __forceinline__ void tmem_cp_128x128b(uint32_t taddr, uint64_t smem_desc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
+// tcgen05.ld.sync.aligned.32x32b.x32.b32: each thread of the warp reads 32 consecutive 32-bit
+// columns of its own TMEM lane (lane = 32 * (warp_id % 4) + lane_id).
+__device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait()
+{
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- cluster
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// mapa.shared::cluster: address of the same smem offset in another CTA of the cluster
+__device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t cta_rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_arrive()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait()
+{
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// ------------------------------------------------------------ global memory
+
+// ld.global.nc.L1::no_allocate.v4: streaming 16-byte read of data used once
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+}  // namespace ptx

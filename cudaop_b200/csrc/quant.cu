@@ -1,0 +1,94 @@
+// Activation quantiser: bf16 rows -> E4M3 bytes + one fp32 scale per row (token).
+//   s[r] = max|x[r,:]| / 448  (1.0 for an all-zero row),  q = e4m3_rn_satfinite(x / s[r])
+// Bandwidth-bound: one CTA per row, 16-byte loads, row maximum by warp shuffles + shared
+// memory, second pass re-reads the row (an L2 hit) and writes 8 bytes per 8 inputs.
+#include "common.cuh"
+#include <cuda_fp8.h>
+#include "../../include/b200q.h"
+
+namespace b200q {
+namespace quant {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+__device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d)
+{
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+    return lo | (hi << 16);
+}
+
+__global__ void __launch_bounds__(kThreads)
+quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict__ Q, float* __restrict__ S, int rows,
+                       int cols)
+{
+    __shared__ float wmax[kThreads / 32];
+    __shared__ float s_scale;
+    const int vecs = cols / 8;
+    for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+        const uint4* x = reinterpret_cast<const uint4*>(X + static_cast<size_t>(row) * cols);
+        float mx = 0.0f;
+        for (int v = threadIdx.x; v < vecs; v += kThreads) {
+            const uint4 u = __ldg(x + v);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mx = fmaxf(mx, fmaxf(fabsf(bf16_lo(w[i])), fabsf(bf16_hi(w[i]))));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        if ((threadIdx.x & 31) == 0) wmax[threadIdx.x >> 5] = mx;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m = 0.0f;
+            for (int i = 0; i < kThreads / 32; ++i) m = fmaxf(m, wmax[i]);
+            const float sc = m > 0.0f ? __fdiv_rn(m, 448.0f) : 1.0f;
+            s_scale = sc;
+            S[row] = sc;
+        }
+        __syncthreads();
+        const float sc = s_scale;
+        uint2* q = reinterpret_cast<uint2*>(Q + static_cast<size_t>(row) * cols);
+        for (int v = threadIdx.x; v < vecs; v += kThreads) {
+            const uint4 u = __ldg(x + v);
+            uint2 o;
+            o.x = cvt4_e4m3(__fdiv_rn(bf16_lo(u.x), sc), __fdiv_rn(bf16_hi(u.x), sc), __fdiv_rn(bf16_lo(u.y), sc),
+                            __fdiv_rn(bf16_hi(u.y), sc));
+            o.y = cvt4_e4m3(__fdiv_rn(bf16_lo(u.z), sc), __fdiv_rn(bf16_hi(u.z), sc), __fdiv_rn(bf16_lo(u.w), sc),
+                            __fdiv_rn(bf16_hi(u.w), sc));
+            q[v] = o;
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace quant
+}  // namespace b200q
+
+extern "C" int b200q_quant_rows_e4m3(const void* X, void* Q, float* S, int rows, int cols, void* stream)
+{
+    using namespace b200q;
+    if (X == nullptr || Q == nullptr || S == nullptr) return cudaErrorInvalidValue;
+    if (rows <= 0 || cols <= 0 || cols % 8 != 0) return cudaErrorInvalidValue;
+    if (!aligned16(X) || (reinterpret_cast<uintptr_t>(Q) & 7u) != 0) return cudaErrorInvalidValue;
+    const int sms = num_sms();
+    if (sms <= 0) return cudaErrorInvalidDevice;
+    const int grid = rows < sms * 8 ? rows : sms * 8;
+    quant::quant_rows_e4m3_kernel<<<grid, quant::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(X), static_cast<uint8_t*>(Q), S, rows, cols);
+    return cudaGetLastError();
+}
+
+extern "C" int b200q_status(unsigned int* host_out, int clear)
+{
+    using namespace b200q;
+    if (host_out == nullptr) return cudaErrorInvalidValue;
+    uint32_t* p = status_ptr();
+    if (p == nullptr) return cudaErrorInvalidDevice;
+    cudaError_t e = cudaMemcpy(host_out, p, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    if (clear) e = cudaMemset(p, 0, sizeof(uint32_t));
+    return e;
+}

@@ -1,0 +1,130 @@
+"""Tensor-parallel SwiGLU MLP on FP8 weights — one process per GPU.
+
+Same decomposition as the reference's ``nccl_mlp_test`` (op/nccl/nccl_mlp_test.cu:144-196,321-352):
+the first projection is split by output features (column-parallel, no communication), the second
+by input features (row-parallel), the input is replicated, and one sum all-reduce of the partial
+outputs leaves identical replicas on every rank.  Differences that the benchmark configuration
+asks for: SwiGLU instead of GELU, E4M3 weights with one fp32 scale per output channel, bf16
+activations quantised per token, and 1/2/4/8 ranks (``torch.distributed``, NCCL over NVLink)
+instead of two devices driven by one host thread.
+
+Per rank and forward pass:
+  1. quantise X (bf16) per token           -> Xq (E4M3), sx            [b200q_quant_rows_e4m3]
+  2. gate/up GEMM + SwiGLU, fused epilogue -> H  (bf16) [T, I/R]       [b200q_gemm_fp8_swiglu]
+  3. quantise H per token                  -> Hq (E4M3), sh            [b200q_quant_rows_e4m3]
+  4. down GEMM, per-token x per-channel    -> partial Y                [b200q_gemm_fp8_rowcol]
+  5. R > 1: all-reduce(sum) of fp32 partials in token chunks on a side stream, overlapping the
+     next chunk's steps 2-4; then one cast to bf16.
+"""
+from __future__ import annotations
+
+import torch
+
+import cudaop_b200 as ops
+
+
+def shard_mlp_weights(w_gate, s_gate, w_up, s_up, w_down, s_down, rank: int, world: int):
+    """Returns this rank's shard of every weight (works on CPU or CUDA tensors).
+
+    w_gate / w_up are [I, H] (K-contiguous, output feature = row): rank r keeps rows
+    [r*I/R, (r+1)*I/R) and the matching gate/up scales — the output-feature split of
+    op/nccl/nccl_mlp_test.cu:321-340 in the [out, in] layout.  w_down is [H, I]: rank r keeps
+    input features (columns) [r*I/R, (r+1)*I/R), re-packed contiguously; its per-output-channel
+    scales are not split — the input-feature split of op/nccl/nccl_mlp_test.cu:342-352.
+    """
+    I = w_gate.shape[0]
+    if I % world != 0:
+        raise ValueError(f"intermediate size {I} is not divisible by {world} ranks")
+    loc = I // world
+    lo, hi = rank * loc, (rank + 1) * loc
+    return (w_gate[lo:hi].contiguous(), s_gate[lo:hi].contiguous(),
+            w_up[lo:hi].contiguous(), s_up[lo:hi].contiguous(),
+            w_down[:, lo:hi].contiguous(), s_down.contiguous())
+
+
+class TensorParallelMLP:
+    """Y = down( silu(X Wg^T) * (X Wu^T) ), weights E4M3 with per-output-channel scales."""
+
+    def __init__(self, w_gate, s_gate, w_up, s_up, w_down, s_down, rank: int = 0, world: int = 1,
+                 group=None, device=None, max_tokens: int = 4096, chunks: int | None = None,
+                 presharded: bool = False):
+        self.rank, self.world, self.group = rank, world, group
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        if presharded:      # the caller already holds only this rank's shard
+            sh = (w_gate, s_gate, w_up, s_up, w_down, s_down)
+        else:
+            sh = shard_mlp_weights(w_gate, s_gate, w_up, s_up, w_down, s_down, rank, world)
+        (self.wg, self.sg, self.wu, self.su, self.wd, self.sd) = [t.to(self.device) for t in sh]
+        self.hidden = self.wg.shape[1]
+        self.inter_local = self.wg.shape[0]
+        self.max_tokens = max_tokens
+        self.chunks = chunks if chunks is not None else (1 if world == 1 else 4)
+        T, H, Il = max_tokens, self.hidden, self.inter_local
+        dev = self.device
+        # workspaces: allocated once, reused by every forward
+        self.xq = torch.empty((T, H), dtype=torch.uint8, device=dev)
+        self.sx = torch.empty((T,), dtype=torch.float32, device=dev)
+        self.h = torch.empty((T, Il), dtype=torch.bfloat16, device=dev)
+        self.hq = torch.empty((T, Il), dtype=torch.uint8, device=dev)
+        self.shs = torch.empty((T,), dtype=torch.float32, device=dev)
+        self.partial = torch.empty((T, H), dtype=torch.float32, device=dev) if world > 1 else None
+        self.comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+        self.kernel_launches_per_forward = 0
+        self.top_kernel_events = None     # set to a list to collect (start, end) events of the gate/up kernel
+
+    def _stage(self, x, y, lo, hi):
+        """Steps 1-4 for tokens [lo, hi) on the current stream; returns the number of launches."""
+        L = ops.lib(); st = torch.cuda.current_stream().cuda_stream
+        n = hi - lo
+        H, Il = self.hidden, self.inter_local
+        xq, sx, h, hq, shs = self.xq[lo:hi], self.sx[lo:hi], self.h[lo:hi], self.hq[lo:hi], self.shs[lo:hi]
+        ops._raise(L.b200q_quant_rows_e4m3(x[lo:hi].data_ptr(), xq.data_ptr(), sx.data_ptr(), n, H, st), "quant x")
+        ev = self.top_kernel_events
+        if ev is not None:
+            e0 = torch.cuda.Event(enable_timing=True); e0.record()
+        ops._raise(L.b200q_gemm_fp8_swiglu(xq.data_ptr(), self.wg.data_ptr(), self.wu.data_ptr(), h.data_ptr(),
+                                           n, Il, H, sx.data_ptr(), self.sg.data_ptr(), self.su.data_ptr(), st),
+                   "gate/up")
+        if ev is not None:
+            e1 = torch.cuda.Event(enable_timing=True); e1.record()
+            ev.append((e0, e1))
+        ops._raise(L.b200q_quant_rows_e4m3(h.data_ptr(), hq.data_ptr(), shs.data_ptr(), n, Il, st), "quant h")
+        if self.world == 1:
+            ops._raise(L.b200q_gemm_fp8_rowcol(hq.data_ptr(), self.wd.data_ptr(), y[lo:hi].data_ptr(), n, H, Il,
+                                               shs.data_ptr(), self.sd.data_ptr(), 0, st), "down")
+        else:
+            ops._raise(L.b200q_gemm_fp8_rowcol(hq.data_ptr(), self.wd.data_ptr(), self.partial[lo:hi].data_ptr(),
+                                               n, H, Il, shs.data_ptr(), self.sd.data_ptr(), 1, st), "down")
+        return 4
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        ops._check(x, "x", (torch.bfloat16,), 2)
+        T, H = x.shape
+        if H != self.hidden or T > self.max_tokens:
+            raise ValueError(f"x must be [<= {self.max_tokens}, {self.hidden}]")
+        y = out if out is not None else torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
+        launches = 0
+        with torch.cuda.device(self.device):
+            if self.world == 1:
+                launches += self._stage(x, y, 0, T)
+            else:
+                import torch.distributed as dist
+                main = torch.cuda.current_stream()
+                nch = max(1, min(self.chunks, T))
+                bounds = [T * i // nch for i in range(nch + 1)]
+                self.comm_stream.wait_stream(main)
+                for c in range(nch):
+                    lo, hi = bounds[c], bounds[c + 1]
+                    if hi == lo:
+                        continue
+                    launches += self._stage(x, y, lo, hi)
+                    done = torch.cuda.Event(); done.record(main)
+                    with torch.cuda.stream(self.comm_stream):
+                        self.comm_stream.wait_event(done)
+                        dist.all_reduce(self.partial[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
+                        y[lo:hi].copy_(self.partial[lo:hi])     # fp32 -> bf16, round-to-nearest-even
+                main.wait_stream(self.comm_stream)
+        self.kernel_launches_per_forward = launches
+        return y
+
+    __call__ = forward

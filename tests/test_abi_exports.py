@@ -1,0 +1,44 @@
+"""The C-ABI library loads without a GPU and exports every symbol the public header declares."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = []
+    for f in os.listdir(os.path.join(ROOT, "include")):
+        if f.endswith(".h"):
+            src = open(os.path.join(ROOT, "include", f)).read()
+            src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+            names += re.findall(r"\b(?:int|void)\s+(b200q_\w+)\s*\(", src)
+    return sorted(set(names))
+
+
+def test_library_exports_every_declared_symbol():
+    import __graft_entry__ as g
+    g.build()
+    import cudaop_b200 as ops
+    lib = ctypes.CDLL(ops.LIB_PATH)
+    names = declared_symbols()
+    assert len(names) >= 6
+    for n in names:
+        assert hasattr(lib, n), f"{n} is declared in include/ but not exported"
+
+
+def test_python_signatures_cover_the_header():
+    import cudaop_b200 as ops
+    for n in declared_symbols():
+        assert n in ops._SIGNATURES, n
+
+
+def test_missing_library_is_a_loud_error(monkeypatch):
+    import cudaop_b200 as ops
+    monkeypatch.setattr(ops, "_lib", None)
+    monkeypatch.setattr(ops, "LIB_PATH", "/nonexistent/libb200q.so")
+    try:
+        ops.lib()
+        assert False, "expected ImportError"
+    except ImportError:
+        pass

@@ -1,0 +1,90 @@
+"""Parity of the INT4 weight-only decode GEMM and of the activation quantiser."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests.util import CORES, assert_bar, bf16_to_f32, dev
+
+pytestmark = pytest.mark.gpu
+
+
+def _w4_ref(xb, wq, s, group=128):
+    return oracle.gemm_f32(oracle.decode_bf16(xb), oracle.dequant_w4(wq, s, group), threads=CORES)
+
+
+@pytest.mark.parametrize("M", [1, 16])
+def test_config_decode_4096(M):
+    # M in {1,16}, N=K=4096, ints in [-8,7], group 128 fp16 scales U(0.005,0.02), bf16 N(0,1) activations
+    import cudaop_b200 as ops
+    xb, wq, s = oracle.make_w4a16_case(M, 4096, 4096, seed=0)
+    out = ops.gemm_w4a16(dev(xb, torch.bfloat16), dev(wq), dev(s, torch.float16))
+    torch.cuda.synchronize()
+    rep = assert_bar(bf16_to_f32(out), _w4_ref(xb, wq, s), 4096, f"w4a16 M={M}")
+    print("w4a16", M, rep)
+
+
+def test_int4_known_answer_is_exact():
+    # op/test/arch_primitives/ptx_mma_integer.cu:61-74: coordinate-dependent S4 values, exact result
+    import cudaop_b200 as ops
+    M, N, K = 16, 40, 256
+    W = np.array([[((n * 5 + k * 3 + 2) % 15) - 7 for k in range(K)] for n in range(N)], np.int8)
+    X = np.array([[((m * 2 + k * 7 + 4) % 15) - 7 for k in range(K)] for m in range(M)], np.float32)
+    s = np.full((N, K // 128), 1.0, np.float32)
+    s[:, 1] = 0.5
+    out = ops.gemm_w4a16(dev(oracle.encode_bf16(X), torch.bfloat16), dev(oracle.pack_s4(W)),
+                         dev(oracle.encode_f16(s), torch.float16))
+    torch.cuda.synchronize()
+    want = X[:, :128] @ W[:, :128].T.astype(np.float32) + 0.5 * (X[:, 128:] @ W[:, 128:].T.astype(np.float32))
+    assert np.array_equal(bf16_to_f32(out), oracle.decode_bf16(oracle.encode_bf16(want)))
+
+
+@pytest.mark.parametrize("shape", [(1, 32, 128), (3, 33, 256), (16, 100, 1024), (17, 64, 384), (40, 4096, 2048),
+                                   (2, 11008, 4096)])
+def test_ragged_shapes(shape):
+    import cudaop_b200 as ops
+    M, N, K = shape
+    xb, wq, s = oracle.make_w4a16_case(M, N, K, seed=M * 7 + N)
+    out = ops.gemm_w4a16(dev(xb, torch.bfloat16), dev(wq), dev(s, torch.float16))
+    torch.cuda.synchronize()
+    assert_bar(bf16_to_f32(out), _w4_ref(xb, wq, s), K, str(shape))
+
+
+def test_w4a16_is_deterministic():
+    import cudaop_b200 as ops
+    xb, wq, s = oracle.make_w4a16_case(16, 4096, 4096, seed=5)
+    x, w, sc = dev(xb, torch.bfloat16), dev(wq), dev(s, torch.float16)
+    a = ops.gemm_w4a16(x, w, sc); b = ops.gemm_w4a16(x, w, sc)
+    assert torch.equal(a, b)
+
+
+def test_w4a16_argument_errors():
+    import cudaop_b200 as ops
+    L = ops.lib()
+    x = torch.zeros(1, 256, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(32, 128, dtype=torch.uint8, device="cuda")
+    s = torch.zeros(32, 2, dtype=torch.float16, device="cuda")
+    y = torch.zeros(1, 32, dtype=torch.bfloat16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert L.b200q_gemm_w4a16(x.data_ptr(), w.data_ptr(), s.data_ptr(), y.data_ptr(), 1, 32, 256, 64, st) == 1
+    assert L.b200q_gemm_w4a16(x.data_ptr(), None, s.data_ptr(), y.data_ptr(), 1, 32, 256, 128, st) == 1
+    assert L.b200q_gemm_w4a16(x.data_ptr(), w.data_ptr(), s.data_ptr(), y.data_ptr(), 1, 32, 200, 128, st) == 1
+    assert L.b200q_gemm_w4a16(x.data_ptr(), w.data_ptr(), s.data_ptr(), y.data_ptr(), 1, 32, 256, 128, st) == 0
+    torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("shape", [(1, 8), (7, 64), (300, 8192), (64, 28672), (33, 3584)])
+def test_activation_quantiser_is_bit_exact(shape):
+    import cudaop_b200 as ops
+    rows, cols = shape
+    rng = np.random.default_rng(rows + cols)
+    xb = oracle.encode_bf16(rng.standard_normal((rows, cols), dtype=np.float32) * rng.uniform(0.01, 30, (rows, 1)).astype(np.float32))
+    if rows > 2:
+        xb[2] = 0          # an all-zero row: scale 1, all zeros
+    q, s = ops.quant_rows_e4m3(dev(xb, torch.bfloat16))
+    torch.cuda.synchronize()
+    q_ref, s_ref = oracle.quant_rows_e4m3(oracle.decode_bf16(xb))
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), s_ref.view(np.uint32))
+    qn = q.cpu().numpy()
+    same = (qn == q_ref) | (((qn & 0x7F) == 0) & ((q_ref & 0x7F) == 0))     # +0 / -0
+    assert same.all()
