@@ -20,17 +20,25 @@ LIB_PATH = os.path.join(_HERE, "libb200q.so")
 _lib = None
 
 __all__ = [
-    "lib", "gemm_fp8", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "gemm_nvfp4",
+    "lib", "gemm_fp8", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "gemm_nvfp4", "nvfp4_swizzle_sf",
     "gemm_sparse_fp8", "quant_rows_e4m3", "status", "LIB_PATH",
 ]
 
 _VP, _I, _F = C.c_void_p, C.c_int, C.c_float
+_SIZE_T_FUNCS = {
+    "b200q_gemm_nvfp4_workspace_bytes": [C.c_int, C.c_int, C.c_int],
+    "b200q_nvfp4_sf_bytes": [C.c_int, C.c_int],
+}
 _SIGNATURES = {
     "b200q_gemm_fp8": [_VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
     "b200q_gemm_fp8_rowcol": [_VP, _VP, _VP, _I, _I, _I, _VP, _VP, _I, _VP],
     "b200q_gemm_fp8_swiglu": [_VP, _VP, _VP, _VP, _I, _I, _I, _VP, _VP, _VP, _VP],
     "b200q_gemm_w4a16": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP],
-    "b200q_gemm_nvfp4": [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
+    "b200q_gemm_nvfp4": [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP, _VP],
+    "b200q_gemm_nvfp4_blocked": [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
+    "b200q_nvfp4_swizzle_sf": [_VP, _VP, _I, _I, _VP],
+    "b200q_nvfp4_set_tile_n": [_I],
+    "b200q_sp24_set_tile_n": [_I],
     "b200q_gemm_sp24_fp8": [_VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
     "b200q_quant_rows_e4m3": [_VP, _VP, _VP, _I, _I, _VP],
     "b200q_status": [_VP, _I],
@@ -49,6 +57,11 @@ def lib() -> C.CDLL:
             if hasattr(L, name):
                 fn = getattr(L, name)
                 fn.restype = _I
+                fn.argtypes = args
+        for name, args in _SIZE_T_FUNCS.items():
+            if hasattr(L, name):
+                fn = getattr(L, name)
+                fn.restype = C.c_size_t
                 fn.argtypes = args
         _lib = L
     return _lib
@@ -148,18 +161,49 @@ def gemm_w4a16(x, wq, scales, group: int = 128) -> torch.Tensor:
     return out
 
 
-def gemm_nvfp4(aq, sfa, bq, sfb, global_a: float, global_b: float) -> torch.Tensor:
-    """C[M,N] (bf16) for NVFP4 operands: packed E2M1 [rows,K/2] + UE4M3 scales [rows,K/16] + global scales."""
-    for n, t in (("aq", aq), ("sfa", sfa), ("bq", bq), ("sfb", sfb)):
-        _check(t, n, (torch.uint8,), 2)
-    _same_device(aq, sfa, bq, sfb)
+def nvfp4_swizzle_sf(sf: torch.Tensor, K: int) -> torch.Tensor:
+    """Row-major UE4M3 scales [rows, K/16] -> the blocked layout the GEMM reads (rewrite weights once)."""
+    _check(sf, "sf", (torch.uint8,), 2)
+    rows = sf.shape[0]
+    if sf.shape[1] * 16 != K or K % 64 != 0:
+        raise ValueError("scales must be [rows, K/16] with K % 64 == 0")
+    out = torch.empty((lib().b200q_nvfp4_sf_bytes(rows, K),), dtype=torch.uint8, device=sf.device)
+    with torch.cuda.device(sf.device):
+        _raise(lib().b200q_nvfp4_swizzle_sf(sf.data_ptr(), out.data_ptr(), rows, K, _stream()), "b200q_nvfp4_swizzle_sf")
+    return out
+
+
+def gemm_nvfp4(aq, sfa, bq, sfb, global_a: float, global_b: float, blocked: bool = False) -> torch.Tensor:
+    """C[M,N] (bf16) for NVFP4 operands: packed E2M1 [rows,K/2], UE4M3 scales, fp32 global scales.
+
+    Scales are row-major [rows, K/16] (``blocked=False``; a scratch buffer for their blocked copy is
+    allocated per call) or the output of :func:`nvfp4_swizzle_sf` (``blocked=True``).
+    """
+    _check(aq, "aq", (torch.uint8,), 2); _check(bq, "bq", (torch.uint8,), 2)
     M, K2 = aq.shape; N, K2b = bq.shape; K = 2 * K2
-    if K2 != K2b or tuple(sfa.shape) != (M, K // 16) or tuple(sfb.shape) != (N, K // 16):
-        raise ValueError("shape mismatch")
+    if K2 != K2b or K % 64 != 0:
+        raise ValueError("shape mismatch (K must match and be a multiple of 64)")
+    L = lib()
     out = torch.empty((M, N), dtype=torch.bfloat16, device=aq.device)
+    if blocked:
+        _check(sfa, "sfa", (torch.uint8,), 1); _check(sfb, "sfb", (torch.uint8,), 1)
+        _same_device(aq, sfa, bq, sfb)
+        if sfa.numel() != L.b200q_nvfp4_sf_bytes(M, K) or sfb.numel() != L.b200q_nvfp4_sf_bytes(N, K):
+            raise ValueError("blocked scale arrays have the wrong size")
+        with torch.cuda.device(aq.device):
+            _raise(L.b200q_gemm_nvfp4_blocked(aq.data_ptr(), sfa.data_ptr(), bq.data_ptr(), sfb.data_ptr(),
+                                              out.data_ptr(), M, N, K, float(global_a), float(global_b), _stream()),
+                   "b200q_gemm_nvfp4_blocked")
+        return out
+    _check(sfa, "sfa", (torch.uint8,), 2); _check(sfb, "sfb", (torch.uint8,), 2)
+    _same_device(aq, sfa, bq, sfb)
+    if tuple(sfa.shape) != (M, K // 16) or tuple(sfb.shape) != (N, K // 16):
+        raise ValueError("shape mismatch")
+    ws = torch.empty((L.b200q_gemm_nvfp4_workspace_bytes(M, N, K),), dtype=torch.uint8, device=aq.device)
     with torch.cuda.device(aq.device):
-        _raise(lib().b200q_gemm_nvfp4(aq.data_ptr(), sfa.data_ptr(), bq.data_ptr(), sfb.data_ptr(), out.data_ptr(),
-                                      M, N, K, float(global_a), float(global_b), _stream()), "b200q_gemm_nvfp4")
+        _raise(L.b200q_gemm_nvfp4(aq.data_ptr(), sfa.data_ptr(), bq.data_ptr(), sfb.data_ptr(), out.data_ptr(),
+                                  M, N, K, float(global_a), float(global_b), ws.data_ptr(), _stream()),
+               "b200q_gemm_nvfp4")
     return out
 
 

@@ -19,6 +19,8 @@
 #ifndef B200Q_H
 #define B200Q_H
 
+#include <stddef.h>
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -51,6 +53,38 @@ int b200q_gemm_fp8_swiglu(const void* X, const void* Wgate, const void* Wup, voi
  * Requires group == 128, K % 128 == 0, 16-byte aligned X and Wq. */
 int b200q_gemm_w4a16(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K,
                      int group, void* stream);
+
+/* NVFP4 block-scaled GEMM: C(bf16) = ((A.sfa) * (B.sfb)^T) * (global_a * global_b).
+ * Aq[M,K/2], Bq[N,K/2]: two E2M1 per byte, low nibble = lower K; SFA[M,K/16], SFB[N,K/16]: one
+ * UE4M3 scale per 16 consecutive K, row-major.  Formats, packing and scale rule:
+ * op/test/arch_primitives/ptx_mma_fp4.cu:49-65,120-144,285-324.  Requires K % 64 == 0 and 16-byte
+ * aligned pointers.  `workspace` is caller-owned scratch of b200q_gemm_nvfp4_workspace_bytes(M,N,K)
+ * bytes: the call first rewrites both scale arrays into the blocked layout the tensor core
+ * reads (b200q_nvfp4_swizzle_sf), then runs the GEMM on them; all on `stream`. */
+int b200q_gemm_nvfp4(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C,
+                     int M, int N, int K, float global_a, float global_b, void* workspace, void* stream);
+size_t b200q_gemm_nvfp4_workspace_bytes(int M, int N, int K);
+
+/* The same GEMM on scales that are already in the blocked layout (weights: rewrite once, reuse).
+ * Blocked layout: [ceil(rows/128)][K/64] blocks of 512 bytes; inside a block the four scales of
+ * row r (K-steps of 16 inside a 64-wide slab) sit at byte (r % 32) * 16 + (r / 32) * 4. */
+int b200q_gemm_nvfp4_blocked(const void* Aq, const void* SFA_blocked, const void* Bq, const void* SFB_blocked,
+                             void* C, int M, int N, int K, float global_a, float global_b, void* stream);
+int b200q_nvfp4_swizzle_sf(const void* sf_rowmajor, void* sf_blocked, int rows, int K, void* stream);
+size_t b200q_nvfp4_sf_bytes(int rows, int K);      /* size of one blocked scale array */
+
+/* 2:4 structured-sparse FP8 GEMM: C(bf16) = (expand(Acomp, Ameta) * B^T) * (scale_a * scale_b).
+ * Acomp[M,K/2] E4M3 keeps the two retained values of every four in order; Ameta[M,K/8]: one
+ * nibble per group of four = two ascending 2-bit positions, lower position in bits [1:0],
+ * nibbles packed low-first (op/test/arch_primitives/ptx_mma_sparse.cu:53-64,163-184).  The
+ * result equals the dense product with the expanded A (ptx_mma_sparse.cu:416-434).
+ * Requires K % 128 == 0 and 16-byte aligned pointers. */
+int b200q_gemm_sp24_fp8(const void* Acomp, const void* Ameta, const void* B, void* C, int M, int N, int K,
+                        float scale_a, float scale_b, void* stream);
+
+/* Tuning knobs (process-wide): width of the B tile, 128 / 192 / 256 columns. */
+int b200q_nvfp4_set_tile_n(int bn);
+int b200q_sp24_set_tile_n(int bn);
 
 /* Activation quantiser: X[rows,cols] bf16 -> Q[rows,cols] E4M3 and S[rows] fp32,
  * S[r] = max|X[r,:]| / 448 (1 for a zero row), Q = rn_satfinite(X / S[r]).  No counterpart in

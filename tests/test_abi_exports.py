@@ -12,7 +12,7 @@ def declared_symbols():
         if f.endswith(".h"):
             src = open(os.path.join(ROOT, "include", f)).read()
             src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
-            names += re.findall(r"\b(?:int|void)\s+(b200q_\w+)\s*\(", src)
+            names += re.findall(r"\b(?:int|void|size_t)\s+(b200q_\w+)\s*\(", src)
     return sorted(set(names))
 
 
@@ -30,7 +30,7 @@ def test_library_exports_every_declared_symbol():
 def test_python_signatures_cover_the_header():
     import cudaop_b200 as ops
     for n in declared_symbols():
-        assert n in ops._SIGNATURES, n
+        assert n in ops._SIGNATURES or n in ops._SIZE_T_FUNCS, n
 
 
 def test_missing_library_is_a_loud_error(monkeypatch):

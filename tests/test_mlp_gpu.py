@@ -80,10 +80,11 @@ def test_two_rank_shards_sum_to_the_single_rank_result():
     # the sharded gate/up outputs are exactly the column blocks of the un-sharded one
     assert torch.equal(torch.cat(hs, dim=1), full.h)
     y2 = acc.to(torch.bfloat16).float()
-    # per-rank token scales differ from the single-rank ones, so the results agree to quantisation
-    # accuracy, not bit for bit
+    # per-rank token scales differ from the single-rank ones, so H is quantised to E4M3 (3 mantissa
+    # bits, ~2-3 % per element) on two different grids: the two results agree to that accuracy,
+    # not bit for bit
     rel = ((y2 - y1).norm() / y1.norm()).item()
-    assert rel < 2e-2, rel
+    assert rel < 5e-2, rel
     # and against the oracle on each rank's own quantised bytes, at the acceptance bar
     ref = np.zeros((T, H), np.float32)
     for r in range(2):
