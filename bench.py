@@ -234,6 +234,10 @@ def gemm_cases(peaks):
 
 
 def run_ours(args):
+    # everything that libraries print (NCCL's version banner, warnings) goes to stderr: stdout
+    # carries the one JSON line only
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     import torch
     import torch.distributed as dist
     import cudaop_b200 as ops
@@ -268,7 +272,8 @@ def run_ours(args):
     wd = rand_e4m3(HIDDEN, loc, 3000 + rank)
     sg = rand_scale(loc, 4000 + rank); su = rand_scale(loc, 5000 + rank); sd = rand_scale(HIDDEN, 6000)
     mlp = TensorParallelMLP(wg, sg, wu, su, wd, sd, rank=rank, world=world, device=dev, max_tokens=TOKENS,
-                            chunks=args.chunks if world > 1 else 1, presharded=True)
+                            chunks=args.chunks if world > 1 else 1, presharded=True, comm=args.comm,
+                            ar_ctas=args.ar_ctas)
     del wg, wu, wd
 
     gen.manual_seed(7)
@@ -305,7 +310,7 @@ def run_ours(args):
         sampler.start()
     # ---- device-resident steps (the headline `value`) with events around the top kernel
     mlp.top_kernel_events = []
-    ms_step = timed(lambda: mlp.forward(x, out=y), args.steps, args.warmup)
+    ms_step = timed(lambda: mlp.forward(x), args.steps, args.warmup)
     evs = mlp.top_kernel_events; mlp.top_kernel_events = None
     torch.cuda.synchronize()
     top_ms = [a.elapsed_time(b) for a, b in evs[-args.steps * max(1, mlp.chunks if world > 1 else 1):]]
@@ -313,8 +318,7 @@ def run_ours(args):
     # ---- end to end: pinned host input -> device, forward, result back to pinned host memory
     def e2e_step():
         x.copy_(x_host, non_blocking=True)
-        mlp.forward(x, out=y)
-        y_host.copy_(y, non_blocking=True)
+        y_host.copy_(mlp.forward(x), non_blocking=True)
     ms_e2e = timed(e2e_step, args.steps, args.warmup)
     clocks = sampler.stop() if sampler else None
     assert ops.status() == 0, "a kernel gave up on a bounded wait"
@@ -333,7 +337,8 @@ def run_ours(args):
         "metric": "tp_mlp_tokens_per_s", "value": TOKENS / (ms_step * 1e-3), "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 acc -> bf16",
-        "data": "synthetic", "config": workload_config(world),
+        "data": "synthetic", "config": dict(workload_config(world), comm=mlp.comm,
+                                             multicast=getattr(mlp, "multicast", None), chunks=mlp.chunks),
         "tflops": MLP_FLOPS / (ms_step * 1e-3) / 1e12,
         "clocks": clocks,
         "e2e": {"value": TOKENS / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
@@ -361,7 +366,7 @@ def run_ours(args):
                                 "kind": "reference" if use_ref else "port",
                                 "sample": f"{args.cpu_tokens} of {TOKENS} tokens through the whole MLP, "
                                           f"{dt:.1f} s, {MLP_FLOPS / TOKENS * args.cpu_tokens / dt / 1e9:.2f} GFLOP/s"}
-    print(json.dumps(line))
+    os.write(real_stdout, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.barrier(); dist.destroy_process_group()
 
@@ -373,6 +378,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chunks", type=int, default=4, help="token chunks for all-reduce overlap (N > 1)")
+    ap.add_argument("--comm", default="auto", choices=["auto", "symm", "nccl"],
+                    help="all-reduce: the library's NVSwitch kernel over symmetric memory, or NCCL")
+    ap.add_argument("--ar-ctas", type=int, default=32)
     ap.add_argument("--cpu-tokens", type=int, default=64, help="tokens in the CPU-baseline sample")
     ap.add_argument("--no-cases", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

@@ -28,6 +28,7 @@ _VP, _I, _F = C.c_void_p, C.c_int, C.c_float
 _SIZE_T_FUNCS = {
     "b200q_gemm_nvfp4_workspace_bytes": [C.c_int, C.c_int, C.c_int],
     "b200q_nvfp4_sf_bytes": [C.c_int, C.c_int],
+    "b200q_allreduce_signal_bytes": [],
 }
 _SIGNATURES = {
     "b200q_gemm_fp8": [_VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
@@ -42,6 +43,7 @@ _SIGNATURES = {
     "b200q_gemm_sp24_fp8": [_VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
     "b200q_quant_rows_e4m3": [_VP, _VP, _VP, _I, _I, _VP],
     "b200q_status": [_VP, _I],
+    "b200q_allreduce_f32_to_bf16": [_VP, _VP, _VP, _VP, _VP, C.c_longlong, C.c_longlong, _I, _I, C.c_uint, C.c_uint, _I, _VP],
 }
 
 

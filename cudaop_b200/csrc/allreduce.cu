@@ -1,0 +1,170 @@
+// Sum all-reduce of the tensor-parallel MLP's partial outputs, written for NVSwitch:
+//   Y (bf16, replicated on every rank) = sum over ranks of P_r (fp32 partial of the down projection)
+// It takes the place of the in-place ncclAllReduce(ncclFloat, ncclSum) of the reference's
+// nccl_mlp_test (op/nccl/nccl_mlp_test.cu:181-195) and keeps its contract: fp32 accumulation and
+// bit-identical replicas (each output element is reduced by exactly one rank and then broadcast;
+// the reference asserts rank0 == rank1, :646-664).
+//
+// One kernel per rank, all ranks running it at the same time on their own GPUs:
+//   1. start barrier over flags in every rank's signal pad (st.release.sys / ld.acquire.sys);
+//   2. rank r reduces elements [r*n/R, (r+1)*n/R): with a multicast mapping one
+//      multimem.ld_reduce.add.v4.f32 per 16 bytes lets the switch add the R partials in flight,
+//      otherwise R plain peer loads are added in rank order; the fp32 sum is rounded once to bf16
+//      and stored to every rank's output (multimem.st, or R peer stores);
+//   3. end barrier, so a rank's Y is complete when its kernel ends.
+// Plain loads/stores and multimem only: no TMA touches peer memory.  Every flag wait is bounded;
+// on a timeout the kernel records it in the status word and returns.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "../../include/b200q.h"
+
+namespace b200q {
+namespace ar {
+
+constexpr int kThreads = 512;
+constexpr int kMaxWorld = 16;
+constexpr int kMaxCtas = 128;
+
+struct Params {
+    const float* const* partial_ptrs;     // device array [world]: every rank's partial buffer
+    __nv_bfloat16* const* out_ptrs;       // device array [world]: every rank's output buffer
+    uint32_t* const* signal_ptrs;         // device array [world]: every rank's signal pad
+    const float* partial_mc;              // multicast address of the partial buffers, or nullptr
+    __nv_bfloat16* out_mc;                // multicast address of the output buffers, or nullptr
+    long long offset, elems;              // element range of this call (same on every rank)
+    uint32_t epoch;                       // strictly increasing per call, same on every rank
+    uint32_t pad_offset_words;            // where this library's flags start inside the signal pad
+    int rank, world;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Barrier between the CTAs with the same index on every rank.  Flags: pad[phase][cta][src_rank].
+// Returns false if a peer did not arrive within the wait limit.
+__device__ __forceinline__ bool rank_barrier(const Params& p, int phase, bool& ok_shared_unused)
+{
+    __syncthreads();
+    bool ok = true;
+    if (threadIdx.x < p.world) {
+        const int peer = threadIdx.x;
+        const size_t slot = p.pad_offset_words + (static_cast<size_t>(phase) * kMaxCtas + blockIdx.x) * kMaxWorld;
+        __threadfence_system();
+        st_release_sys(p.signal_ptrs[peer] + slot + p.rank, p.epoch);
+        const uint32_t* mine = p.signal_ptrs[p.rank] + slot + peer;
+        const unsigned long long t0 = ptx::globaltimer_ns();
+        uint32_t spins = 0;
+        // flags only grow; the signed difference tolerates wrap-around of the epoch counter
+        while (static_cast<int32_t>(ld_acquire_sys(mine) - p.epoch) < 0) {
+            if ((++spins & 0x3Fu) == 0 && ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
+                atomicCAS(p.status, 0u, ptx::kStatusTimeout | ((16u + phase) << 24) | (blockIdx.x & 0xFFFFFFu));
+                ok = false;
+                break;
+            }
+        }
+    }
+    (void)ok_shared_unused;
+    return __syncthreads_and(ok);
+}
+
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc)
+{
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(mc)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ void multimem_st_bf16x8(__nv_bfloat16* mc, uint4 v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+
+template <bool MC>
+__global__ void __launch_bounds__(kThreads)
+allreduce_f32_to_bf16_kernel(const Params p)
+{
+    bool dummy = true;
+    if (!rank_barrier(p, 0, dummy)) return;
+
+    const long long per = p.elems / p.world;                 // elements this rank reduces
+    const long long base = p.offset + per * p.rank;
+    const long long vecs = per / 8;                           // 8 fp32 in -> 8 bf16 (16 bytes) out
+    for (long long v = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; v < vecs;
+         v += static_cast<long long>(gridDim.x) * kThreads) {
+        const long long e = base + v * 8;
+        float4 a, b;
+        if (MC) {
+            a = multimem_ld_reduce_f32x4(p.partial_mc + e);
+            b = multimem_ld_reduce_f32x4(p.partial_mc + e + 4);
+        } else {
+            a = make_float4(0.f, 0.f, 0.f, 0.f); b = a;
+            for (int r = 0; r < p.world; ++r) {               // fixed rank order
+                const float4* src = reinterpret_cast<const float4*>(p.partial_ptrs[r] + e);
+                const float4 x = __ldcg(src), y = __ldcg(src + 1);
+                a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+                b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+            }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
+        o.z = pack_bf16x2(b.x, b.y); o.w = pack_bf16x2(b.z, b.w);
+        if (MC) {
+            multimem_st_bf16x8(p.out_mc + e, o);
+        } else {
+            for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.out_ptrs[r] + e) = o;
+        }
+    }
+    rank_barrier(p, 1, dummy);
+}
+
+}  // namespace ar
+}  // namespace b200q
+
+extern "C" {
+
+size_t b200q_allreduce_signal_bytes(void)
+{
+    return static_cast<size_t>(2) * b200q::ar::kMaxCtas * b200q::ar::kMaxWorld * sizeof(uint32_t);
+}
+
+int b200q_allreduce_f32_to_bf16(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                void* const* signal_ptrs_dev, const void* partial_multicast, void* out_multicast,
+                                long long elem_offset, long long elems, int rank, int world, unsigned int epoch,
+                                unsigned int signal_offset_bytes, int ctas, void* stream)
+{
+    using namespace b200q;
+    if (partial_ptrs_dev == nullptr || out_ptrs_dev == nullptr || signal_ptrs_dev == nullptr) return cudaErrorInvalidValue;
+    if (world < 1 || world > ar::kMaxWorld || rank < 0 || rank >= world) return cudaErrorInvalidValue;
+    if (elems <= 0 || elem_offset < 0 || elems % (8LL * world) != 0 || elem_offset % 8 != 0) return cudaErrorInvalidValue;
+    if (ctas < 1 || ctas > ar::kMaxCtas || signal_offset_bytes % 4 != 0) return cudaErrorInvalidValue;
+    if ((partial_multicast == nullptr) != (out_multicast == nullptr)) return cudaErrorInvalidValue;
+    ar::Params p{};
+    p.partial_ptrs = reinterpret_cast<const float* const*>(partial_ptrs_dev);
+    p.out_ptrs = reinterpret_cast<__nv_bfloat16* const*>(out_ptrs_dev);
+    p.signal_ptrs = reinterpret_cast<uint32_t* const*>(signal_ptrs_dev);
+    p.partial_mc = static_cast<const float*>(partial_multicast);
+    p.out_mc = static_cast<__nv_bfloat16*>(out_multicast);
+    p.offset = elem_offset; p.elems = elems; p.epoch = epoch; p.pad_offset_words = signal_offset_bytes / 4;
+    p.rank = rank; p.world = world;
+    p.status = status_ptr();
+    if (p.status == nullptr) return cudaErrorInvalidDevice;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (partial_multicast != nullptr) ar::allreduce_f32_to_bf16_kernel<true><<<ctas, ar::kThreads, 0, s>>>(p);
+    else ar::allreduce_f32_to_bf16_kernel<false><<<ctas, ar::kThreads, 0, s>>>(p);
+    return cudaGetLastError();
+}
+
+}  // extern "C"

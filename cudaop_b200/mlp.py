@@ -13,8 +13,11 @@ Per rank and forward pass:
   2. gate/up GEMM + SwiGLU, fused epilogue -> H  (bf16) [T, I/R]       [b200q_gemm_fp8_swiglu]
   3. quantise H per token                  -> Hq (E4M3), sh            [b200q_quant_rows_e4m3]
   4. down GEMM, per-token x per-channel    -> partial Y                [b200q_gemm_fp8_rowcol]
-  5. R > 1: all-reduce(sum) of fp32 partials in token chunks on a side stream, overlapping the
-     next chunk's steps 2-4; then one cast to bf16.
+  5. R > 1: sum all-reduce of the fp32 partials, in token chunks on a side stream so that it
+     overlaps the next chunk's steps 2-4.  Default: the library's own NVSwitch kernel
+     (b200q_allreduce_f32_to_bf16: multimem.ld_reduce in the switch, one rounding to bf16,
+     multimem.st broadcast) over torch symmetric memory; ``comm="nccl"`` uses
+     torch.distributed.all_reduce + a cast instead.
 """
 from __future__ import annotations
 
@@ -47,7 +50,7 @@ class TensorParallelMLP:
 
     def __init__(self, w_gate, s_gate, w_up, s_up, w_down, s_down, rank: int = 0, world: int = 1,
                  group=None, device=None, max_tokens: int = 4096, chunks: int | None = None,
-                 presharded: bool = False):
+                 presharded: bool = False, comm: str = "auto", ar_ctas: int = 32):
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
         if presharded:      # the caller already holds only this rank's shard
@@ -67,10 +70,55 @@ class TensorParallelMLP:
         self.h = torch.empty((T, Il), dtype=torch.bfloat16, device=dev)
         self.hq = torch.empty((T, Il), dtype=torch.uint8, device=dev)
         self.shs = torch.empty((T,), dtype=torch.float32, device=dev)
-        self.partial = torch.empty((T, H), dtype=torch.float32, device=dev) if world > 1 else None
+        self.partial = None
         self.comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
+        self.comm = "none"
+        self.ar_ctas = ar_ctas
+        self._epoch = 0
+        if world > 1:
+            self.comm = comm
+            if comm in ("auto", "symm"):
+                try:
+                    self._init_symmetric(T, H)
+                    self.comm = "symm"
+                except Exception:
+                    if comm == "symm":
+                        raise
+                    self.comm = "nccl"
+            if self.comm == "nccl":
+                self.partial = torch.empty((T, H), dtype=torch.float32, device=dev)
         self.kernel_launches_per_forward = 0
         self.top_kernel_events = None     # set to a list to collect (start, end) events of the gate/up kernel
+
+    def _init_symmetric(self, T, H):
+        """Partial sums, output and barrier flags in symmetric memory (peer-mapped on every rank,
+        with an NVSwitch multicast mapping when the fabric offers one)."""
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = self.group if self.group is not None else dist.group.WORLD
+        dev = self.device
+        self.partial = symm.empty((T, H), dtype=torch.float32, device=dev)
+        self.y_sym = symm.empty((T, H), dtype=torch.bfloat16, device=dev)
+        nflags = ops.lib().b200q_allreduce_signal_bytes() // 4
+        self.flags = symm.empty((nflags,), dtype=torch.int32, device=dev)
+        self.flags.zero_()
+        self._hp = symm.rendezvous(self.partial, group)
+        self._hy = symm.rendezvous(self.y_sym, group)
+        self._hf = symm.rendezvous(self.flags, group)
+        self.multicast = bool(self._hp.multicast_ptr) and bool(self._hy.multicast_ptr)
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)
+
+    def _allreduce_chunk(self, lo, hi):
+        """Launches the all-reduce kernel for tokens [lo, hi) on the current stream."""
+        self._epoch += 1
+        H = self.hidden
+        mc_p = self._hp.multicast_ptr if self.multicast else None
+        mc_y = self._hy.multicast_ptr if self.multicast else None
+        ops._raise(ops.lib().b200q_allreduce_f32_to_bf16(
+            self._hp.buffer_ptrs_dev, self._hy.buffer_ptrs_dev, self._hf.buffer_ptrs_dev, mc_p, mc_y,
+            lo * H, (hi - lo) * H, self.rank, self.world, self._epoch, 0, self.ar_ctas,
+            torch.cuda.current_stream().cuda_stream), "b200q_allreduce_f32_to_bf16")
 
     def _stage(self, x, y, lo, hi):
         """Steps 1-4 for tokens [lo, hi) on the current stream; returns the number of launches."""
@@ -102,7 +150,10 @@ class TensorParallelMLP:
         T, H = x.shape
         if H != self.hidden or T > self.max_tokens:
             raise ValueError(f"x must be [<= {self.max_tokens}, {self.hidden}]")
-        y = out if out is not None else torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
+        if self.comm == "symm":
+            y = self.y_sym[:T]
+        else:
+            y = out if out is not None else torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
         launches = 0
         with torch.cuda.device(self.device):
             if self.world == 1:
@@ -121,9 +172,16 @@ class TensorParallelMLP:
                     done = torch.cuda.Event(); done.record(main)
                     with torch.cuda.stream(self.comm_stream):
                         self.comm_stream.wait_event(done)
-                        dist.all_reduce(self.partial[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
-                        y[lo:hi].copy_(self.partial[lo:hi])     # fp32 -> bf16, round-to-nearest-even
+                        if self.comm == "symm":
+                            self._allreduce_chunk(lo, hi)
+                            launches += 1
+                        else:
+                            dist.all_reduce(self.partial[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
+                            y[lo:hi].copy_(self.partial[lo:hi])     # fp32 -> bf16, round-to-nearest-even
                 main.wait_stream(self.comm_stream)
+                if self.comm == "symm" and out is not None:
+                    out[:T].copy_(y)
+                    y = out
         self.kernel_launches_per_forward = launches
         return y
 

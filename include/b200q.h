@@ -91,6 +91,21 @@ int b200q_sp24_set_tile_n(int bn);
  * the reference (its MLP is fp32); needed on either side of the FP8 GEMMs.  cols % 8 == 0. */
 int b200q_quant_rows_e4m3(const void* X, void* Q, float* S, int rows, int cols, void* stream);
 
+/* Sum all-reduce of the MLP's fp32 partial outputs over NVLink / NVSwitch, one call per rank, all
+ * ranks at the same time: Y(bf16, on every rank) = sum_r P_r(fp32).  Replaces the in-place
+ * ncclAllReduce(ncclFloat, ncclSum) of op/nccl/nccl_mlp_test.cu:181-195 with the same contract
+ * (fp32 accumulation, bit-identical replicas).  The three pointer arguments are DEVICE arrays of
+ * `world` pointers to every rank's partial buffer, output buffer and flag buffer (peer-mapped
+ * memory, same layout on every rank; the flag buffer holds b200q_allreduce_signal_bytes() bytes,
+ * zeroed once before the first call).  With multicast addresses of the partial and output buffers
+ * the switch does the additions and the broadcast; pass NULL for both to use plain peer loads and
+ * stores.  `epoch` must grow by one per call, identically on every rank; elems % (8 * world) == 0. */
+int b200q_allreduce_f32_to_bf16(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                void* const* signal_ptrs_dev, const void* partial_multicast, void* out_multicast,
+                                long long elem_offset, long long elems, int rank, int world, unsigned int epoch,
+                                unsigned int signal_offset_bytes, int ctas, void* stream);
+size_t b200q_allreduce_signal_bytes(void);
+
 /* Reads (and optionally clears) the device status word of the current device into *host_out.
  * 0 = no kernel of this library gave up on a bounded wait.  Synchronises the device. */
 int b200q_status(unsigned int* host_out, int clear);

@@ -1,0 +1,61 @@
+"""The NVSwitch all-reduce kernel and the sharded MLP on 2 real GPUs (skipped with fewer).
+One process per GPU, NCCL only for the rendezvous; no rank is ever killed or left waiting."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_two():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+
+
+def _worker(rank, world, port, mode, out_dir):
+    import torch.distributed as dist
+    import cudaop_b200 as ops
+    from cudaop_b200.mlp import TensorParallelMLP
+    import oracle
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    T, H, I = 256, 512, 1024
+    case = oracle.make_mlp_case(T, H, I, seed=31)
+    ts = [torch.from_numpy(np.ascontiguousarray(t)) for t in case[1:]]
+    mlp = TensorParallelMLP(*ts, rank=rank, world=world, max_tokens=T, chunks=2, comm="symm" if mode != "nccl" else "nccl")
+    if mode == "p2p":
+        mlp.multicast = False
+    x = torch.from_numpy(case[0].view(np.int16)).cuda().view(torch.bfloat16)
+    y = mlp(x).clone()
+    y2 = mlp(x).clone()                       # a second pass reuses buffers and flags
+    torch.cuda.synchronize()
+    assert ops.status() == 0
+    assert torch.equal(y, y2)
+    # the kernel's sum against the fp32 partials of both ranks gathered with NCCL
+    parts = [torch.empty_like(mlp.partial) for _ in range(world)]
+    dist.all_gather(parts, mlp.partial.contiguous())
+    want = sum(p for p in parts).to(torch.bfloat16)
+    torch.save({"y": y.cpu(), "want": want.cpu(), "comm": mlp.comm, "mc": getattr(mlp, "multicast", None)},
+               os.path.join(out_dir, f"{mode}_r{rank}.pt"))
+    dist.barrier(); dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("mode", ["multicast", "p2p", "nccl"])
+def test_two_rank_mlp_allreduce(mode, tmp_path):
+    _need_two()
+    import torch.multiprocessing as mp
+    port = 29600 + (os.getpid() % 1000) + {"multicast": 0, "p2p": 1, "nccl": 2}[mode]
+    mp.spawn(_worker, args=(2, port, mode, str(tmp_path)), nprocs=2, join=True)
+    r0 = torch.load(tmp_path / f"{mode}_r0.pt"); r1 = torch.load(tmp_path / f"{mode}_r1.pt")
+    print(mode, "comm:", r0["comm"], "multicast:", r0["mc"])
+    assert torch.equal(r0["y"], r1["y"])                # replicas bit-identical (nccl_mlp_test.cu:646-664)
+    if mode == "nccl":
+        assert torch.equal(r0["y"], r0["want"])
+    else:
+        # one rounding of the fp32 sum; the switch may add in a different order than rank order
+        d = (r0["y"].float() - r0["want"].float()).abs().max().item()
+        assert d <= 2.0 ** -7 * r0["want"].float().abs().max().item()
+        assert (r0["y"] == r0["want"]).float().mean().item() > 0.99
