@@ -378,7 +378,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chunks", type=int, default=4, help="token chunks for all-reduce overlap (N > 1)")
-    ap.add_argument("--comm", default="auto", choices=["auto", "symm", "nccl"],
+    ap.add_argument("--comm", default="auto", choices=["auto", "fused", "symm", "nccl"],
                     help="all-reduce: the library's NVSwitch kernel over symmetric memory, or NCCL")
     ap.add_argument("--ar-ctas", type=int, default=32)
     ap.add_argument("--cpu-tokens", type=int, default=64, help="tokens in the CPU-baseline sample")

@@ -1,4 +1,4 @@
-// Host side of the FP8 GEMM entry points: argument checks, tensor maps, launch.
+// Host side of the FP8 GEMM entry points: argument checks, tile choice, tensor maps, launch.
 #include "gemm_fp8.cuh"
 #include "../../include/b200q.h"
 
@@ -7,17 +7,19 @@ namespace fp8 {
 
 namespace {
 
-template <int EPI, typename OutT>
+int g_force_bn = 0;      // 0 = choose per problem; 224 or 256 = forced (b200q_fp8_set_tile_n)
+
+template <int EPI, typename OutT, int BN, bool AR>
 cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2, const Params& p,
                    cudaStream_t stream)
 {
-    auto kernel = gemm_fp8_kernel<EPI, OutT>;
+    auto kernel = gemm_fp8_kernel<EPI, OutT, BN, AR>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
@@ -25,7 +27,7 @@ cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
     if (sms <= 0) return cudaErrorInvalidDevice;
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sms ? tiles : sms;
-    kernel<<<grid, kThreads, kSmemBytes, stream>>>(tmA, tmB, tmB2, p);
+    kernel<<<grid, kBaseThreads + (AR ? kReducerThreads : 0), Cfg<BN>::kSmemBytes, stream>>>(tmA, tmB, tmB2, p);
     return cudaGetLastError();
 }
 
@@ -40,11 +42,33 @@ bool bad_operands(const void* A, const void* B, const void* C, int M, int N, int
     return false;
 }
 
+// B-tile width: the persistent grid runs ceil(tiles / SMs) waves of tiles whose cost grows with
+// the width; pick the width with the smaller product (224 wins when 256 leaves a ragged last wave).
+int choose_bn(int M, int n_out, bool swiglu)
+{
+    if (g_force_bn) return g_force_bn;
+    const int sms = num_sms() > 0 ? num_sms() : 148;
+    long long best_cost = -1; int best = 256;
+    for (int bn : {256, 224}) {
+        const int out_cols = swiglu ? bn / 2 : bn;
+        const long long tiles = static_cast<long long>((M + kBM - 1) / kBM) * ((n_out + out_cols - 1) / out_cols);
+        const long long cost = ((tiles + sms - 1) / sms) * (bn + 24);     // +24: per-tile fixed cost (fill, drain)
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
 }  // namespace
+
+struct ArArgs {
+    const void* const* partial_ptrs; void* const* out_ptrs; void* const* flag_ptrs;
+    const void* partial_mc; void* out_mc; void* counters;
+    unsigned int flag_offset_bytes, epoch; int rank, world;
+};
 
 cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int epi, int out_f32, float alpha,
                  const float* row_scale, const float* col_scale, const void* B2, const float* col_scale2,
-                 long long ldc, cudaStream_t stream)
+                 long long ldc, const ArArgs* ar, cudaStream_t stream)
 {
     if (bad_operands(A, B, C, M, N, K)) return cudaErrorInvalidValue;
     if (epi == kEpiRowCol && (row_scale == nullptr || col_scale == nullptr)) return cudaErrorInvalidValue;
@@ -53,36 +77,56 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
         return cudaErrorInvalidValue;
     if (ldc < N) return cudaErrorInvalidValue;
 
+    const bool swiglu = epi == kEpiSwiGLU;
+    const int bn = ar ? 256 : choose_bn(M, N, swiglu);
+    const int out_cols = swiglu ? bn / 2 : bn;
     Params p{};
     p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.alpha = alpha;
     p.row_scale = row_scale; p.col_scale = col_scale; p.col_scale2 = col_scale2;
     p.tiles_m = (M + kBM - 1) / kBM;
-    p.tiles_n = (epi == kEpiSwiGLU) ? (N + 127) / 128 : (N + kBN - 1) / kBN;
+    p.tiles_n = (N + out_cols - 1) / out_cols;
+    p.group = 16;
     p.status = status_ptr();
     if (p.status == nullptr) return cudaErrorInvalidDevice;
+    if (ar) {
+        if (epi != kEpiRowCol || !out_f32 || N % 8 != 0 || ldc != N || !aligned16(C)) return cudaErrorInvalidValue;
+        if (ar->partial_ptrs == nullptr || ar->out_ptrs == nullptr || ar->flag_ptrs == nullptr || ar->counters == nullptr)
+            return cudaErrorInvalidValue;
+        if (ar->world < 1 || ar->world > kMaxWorld || ar->rank < 0 || ar->rank >= ar->world) return cudaErrorInvalidValue;
+        if ((ar->partial_mc == nullptr) != (ar->out_mc == nullptr) || ar->flag_offset_bytes % 4 != 0) return cudaErrorInvalidValue;
+        p.group = 4;                                   // 512-row groups finish (and are reduced) early
+        if ((p.tiles_m + p.group - 1) / p.group > kMaxGroups) return cudaErrorInvalidValue;
+        p.partial_ptrs = reinterpret_cast<const float* const*>(ar->partial_ptrs);
+        p.out_ptrs = reinterpret_cast<__nv_bfloat16* const*>(ar->out_ptrs);
+        p.flag_ptrs = reinterpret_cast<uint32_t* const*>(ar->flag_ptrs);
+        p.partial_mc = static_cast<const float*>(ar->partial_mc);
+        p.out_mc = static_cast<__nv_bfloat16*>(ar->out_mc);
+        p.counters = static_cast<uint32_t*>(ar->counters);
+        p.flag_offset_words = ar->flag_offset_bytes / 4; p.epoch = ar->epoch; p.rank = ar->rank; p.world = ar->world;
+        cudaError_t e = cudaMemsetAsync(p.counters, 0, (kMaxGroups + 1) * sizeof(uint32_t), stream);
+        if (e != cudaSuccess) return e;
+    }
 
     CUtensorMap tmA, tmB, tmB2;
-    const uint32_t b_rows = (epi == kEpiSwiGLU) ? 128u : static_cast<uint32_t>(kBN);
+    const uint32_t b_rows = static_cast<uint32_t>(swiglu ? bn / 2 : bn);
     if (!make_tmap_2d_u8(&tmA, A, M, K, K, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
     if (!make_tmap_2d_u8(&tmB, B, N, K, K, b_rows, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
     tmB2 = tmB;
-    if (epi == kEpiSwiGLU &&
-        !make_tmap_2d_u8(&tmB2, B2, N, K, K, b_rows, kBK, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (swiglu && !make_tmap_2d_u8(&tmB2, B2, N, K, K, b_rows, kBK, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;
 
+#define B200Q_LAUNCH(EPI, T, AR_) \
+    (bn == 224 ? launch<EPI, T, 224, AR_>(tmA, tmB, tmB2, p, stream) : launch<EPI, T, 256, AR_>(tmA, tmB, tmB2, p, stream))
+    if (ar) return launch<kEpiRowCol, float, 256, true>(tmA, tmB, tmB2, p, stream);
     switch (epi) {
-    case kEpiTensor:
-        return out_f32 ? launch<kEpiTensor, float>(tmA, tmB, tmB2, p, stream)
-                       : launch<kEpiTensor, __nv_bfloat16>(tmA, tmB, tmB2, p, stream);
-    case kEpiRowCol:
-        return out_f32 ? launch<kEpiRowCol, float>(tmA, tmB, tmB2, p, stream)
-                       : launch<kEpiRowCol, __nv_bfloat16>(tmA, tmB, tmB2, p, stream);
+    case kEpiTensor: return out_f32 ? B200Q_LAUNCH(kEpiTensor, float, false) : B200Q_LAUNCH(kEpiTensor, __nv_bfloat16, false);
+    case kEpiRowCol: return out_f32 ? B200Q_LAUNCH(kEpiRowCol, float, false) : B200Q_LAUNCH(kEpiRowCol, __nv_bfloat16, false);
     case kEpiSwiGLU:
         if (out_f32) return cudaErrorInvalidValue;
-        return launch<kEpiSwiGLU, __nv_bfloat16>(tmA, tmB, tmB2, p, stream);
-    default:
-        return cudaErrorInvalidValue;
+        return B200Q_LAUNCH(kEpiSwiGLU, __nv_bfloat16, false);
+    default: return cudaErrorInvalidValue;
     }
+#undef B200Q_LAUNCH
 }
 
 }  // namespace fp8
@@ -94,21 +138,50 @@ int b200q_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, f
                    void* stream)
 {
     return b200q::fp8::gemm(A, B, C, M, N, K, b200q::fp8::kEpiTensor, 0, scale_a * scale_b, nullptr, nullptr,
-                            nullptr, nullptr, N, static_cast<cudaStream_t>(stream));
+                            nullptr, nullptr, N, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int b200q_gemm_fp8_rowcol(const void* A, const void* B, void* C, int M, int N, int K, const float* row_scale,
                           const float* col_scale, int out_f32, void* stream)
 {
     return b200q::fp8::gemm(A, B, C, M, N, K, b200q::fp8::kEpiRowCol, out_f32, 1.0f, row_scale, col_scale, nullptr,
-                            nullptr, N, static_cast<cudaStream_t>(stream));
+                            nullptr, N, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 int b200q_gemm_fp8_swiglu(const void* X, const void* Wgate, const void* Wup, void* H, int M, int I, int K,
                           const float* row_scale, const float* gate_scale, const float* up_scale, void* stream)
 {
     return b200q::fp8::gemm(X, Wgate, H, M, I, K, b200q::fp8::kEpiSwiGLU, 0, 1.0f, row_scale, gate_scale, Wup,
-                            up_scale, I, static_cast<cudaStream_t>(stream));
+                            up_scale, I, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_gemm_fp8_rowcol_allreduce(const void* A, const void* B, void* partial_local, int M, int N, int K,
+                                    const float* row_scale, const float* col_scale,
+                                    const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                    void* const* flag_ptrs_dev, const void* partial_multicast, void* out_multicast,
+                                    void* counters_local, unsigned int flag_offset_bytes, unsigned int epoch, int rank,
+                                    int world, void* stream)
+{
+    b200q::fp8::ArArgs ar{partial_ptrs_dev, out_ptrs_dev, flag_ptrs_dev, partial_multicast, out_multicast,
+                          counters_local, flag_offset_bytes, epoch, rank, world};
+    return b200q::fp8::gemm(A, B, partial_local, M, N, K, b200q::fp8::kEpiRowCol, 1, 1.0f, row_scale, col_scale,
+                            nullptr, nullptr, N, &ar, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200q_fused_allreduce_flag_bytes(void)
+{
+    return static_cast<size_t>(b200q::fp8::kMaxGroups + 1) * b200q::fp8::kMaxWorld * sizeof(uint32_t);
+}
+size_t b200q_fused_allreduce_counter_bytes(void)
+{
+    return static_cast<size_t>(b200q::fp8::kMaxGroups + 1) * sizeof(uint32_t);
+}
+
+int b200q_fp8_set_tile_n(int bn)
+{
+    if (bn != 0 && bn != 224 && bn != 256) return cudaErrorInvalidValue;
+    b200q::fp8::g_force_bn = bn;
+    return 0;
 }
 
 }  // extern "C"

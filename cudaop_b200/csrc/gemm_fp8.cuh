@@ -1,15 +1,25 @@
 // FP8 E4M3 GEMM for sm_100a:  C[M,N] = epilogue( A[M,K] * B[N,K]^T ), fp32 accumulate.
 //
 // One persistent CTA per SM, 192 threads in three roles:
-//   warp 0    TMA producer  : 128-byte-swizzled A (128 x 128 B) and B (256 x 128 B) tiles into a
-//                             4-stage shared-memory ring, completion on "full" mbarriers
-//   warp 1    MMA issuer    : one elected thread issues tcgen05.mma kind::f8f6f4 (128 x 256 x 32)
+//   warp 0    TMA producer  : 128-byte-swizzled A (128 x 128 B) and B (BN x 128 B) tiles into a
+//                             shared-memory ring, completion on "full" mbarriers
+//   warp 1    MMA issuer    : one elected thread issues tcgen05.mma kind::f8f6f4 (128 x BN x 32)
 //                             reading shared memory through matrix descriptors, accumulating into
 //                             TMEM; tcgen05.commit releases ring slots and publishes accumulators
-//   warps 2-5 epilogue      : tcgen05.ld the 128 x 256 fp32 accumulator (one TMEM lane = one row),
+//   warps 2-5 epilogue      : tcgen05.ld the 128 x BN fp32 accumulator (one TMEM lane = one row),
 //                             apply the scale rule, cast to the output type, 16-byte stores
-// TMEM holds two accumulators (2 x 256 columns), so the epilogue of tile i overlaps the
-// main loop of tile i+1.  No cluster, no multicast.
+// TMEM holds two accumulators, so the epilogue of tile i overlaps the main loop of tile i+1.
+// No cluster, no multicast loads.
+//
+// With the all-reduce fused in (the row-parallel down projection of the tensor-parallel MLP) the
+// CTA has four more warps, the reducers.  The epilogue writes fp32 partial tiles into this rank's
+// symmetric buffer and counts finished tiles per group of tile rows; the warp that completes a
+// group raises this rank's flag for it on every rank; the reducers of every CTA wait until all
+// ranks have raised a group's flag, then add that group's partials across ranks through the
+// NVSwitch (multimem.ld_reduce, or plain peer loads in rank order), round once to bf16 and
+// broadcast the result to every rank (multimem.st, or peer stores).  The reduction of group g runs
+// under the main loop of group g+1; only the last group's reduction is exposed.  It replaces
+// GEMM -> ncclAllReduce of op/nccl/nccl_mlp_test.cu:170-195 by one kernel.
 //
 // Semantics follow the reference: operands K-contiguous, C = A * B^T (op/cpu/cpu_ops.cpp:95-113);
 // per-tensor scales are not MMA operands, the epilogue multiplies the fp32 accumulator
@@ -23,20 +33,27 @@ namespace b200q {
 namespace fp8 {
 
 constexpr int kBM = 128;
-constexpr int kBN = 256;
 constexpr int kBK = 128;           // bytes == elements for FP8: one 128-byte swizzle row
-constexpr int kStages = 4;
-constexpr int kThreads = 192;
-constexpr int kABytes = kBM * kBK;                 // 16 KiB
-constexpr int kBBytes = kBN * kBK;                 // 32 KiB
-constexpr int kStageBytes = kABytes + kBBytes;     // 48 KiB
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int kBaseThreads = 192;
+constexpr int kReducerThreads = 128;
 constexpr uint32_t kTmemCols = 512;
+constexpr int kMaxWorld = 16;
+constexpr int kMaxGroups = 64;     // tile-row groups tracked by the fused all-reduce
+
+template <int BN>
+struct Cfg {
+    static constexpr int kABytes = kBM * kBK;                 // 16 KiB
+    static constexpr int kBBytes = BN * kBK;
+    static constexpr int kStageBytes = kABytes + kBBytes;     // multiple of 1024 for BN % 8 == 0
+    static constexpr int kStages = (227 * 1024 - 1024 - 256) / kStageBytes > 6 ? 6 : (227 * 1024 - 1024 - 256) / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static_assert(kStageBytes % 1024 == 0 && BN % 16 == 0 && BN <= 256, "tile shape");
+};
 
 enum Epilogue : int {
     kEpiTensor = 0,   // C = acc * alpha                                  (per-tensor scales)
     kEpiRowCol = 1,   // C = acc * (row_scale[m] * col_scale[n])          (per-token x per-channel)
-    kEpiSwiGLU = 2,   // B tile = 128 gate rows + 128 up rows; C[m,n] = silu(g) * u, 128 columns per tile
+    kEpiSwiGLU = 2,   // B tile = BN/2 gate rows + BN/2 up rows; C[m,n] = silu(g) * u, BN/2 columns per tile
 };
 
 struct Params {
@@ -48,18 +65,29 @@ struct Params {
     const float* col_scale;      // [N]   (gate scales for SwiGLU)
     const float* col_scale2;     // [N]   (up scales for SwiGLU)
     int tiles_m, tiles_n;
+    int group;                   // tile rows that walk the N tiles together
     uint32_t* status;
+    // fused all-reduce (AR kernels only)
+    const float* const* partial_ptrs;    // device array [world]: every rank's fp32 partial buffer (C is this rank's)
+    __nv_bfloat16* const* out_ptrs;      // device array [world]: every rank's bf16 output
+    uint32_t* const* flag_ptrs;          // device array [world]: every rank's flag buffer
+    const float* partial_mc;             // multicast address of the partial buffers, or nullptr
+    __nv_bfloat16* out_mc;               // multicast address of the outputs, or nullptr
+    uint32_t* counters;                  // local, zeroed before the launch: [kMaxGroups + 1]
+    uint32_t flag_offset_words;
+    uint32_t epoch;
+    int rank, world;
 };
 
 template <typename OutT> struct OutPack;
 template <> struct OutPack<__nv_bfloat16> {
-    // 32 fp32 -> 32 bf16 = 64 bytes
-    static __device__ __forceinline__ void store32(__nv_bfloat16* dst, const float (&v)[32], bool vec, int valid)
+    template <int W>
+    static __device__ __forceinline__ void store(__nv_bfloat16* dst, const float (&v)[W], bool vec, int valid)
     {
         if (vec) {
             uint4* d = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < W / 8; ++i) {
                 uint4 q;
                 q.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
                 q.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
@@ -69,46 +97,98 @@ template <> struct OutPack<__nv_bfloat16> {
             }
         } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
+            for (int i = 0; i < W; ++i)
                 if (i < valid) dst[i] = __float2bfloat16_rn(v[i]);
         }
     }
 };
 template <> struct OutPack<float> {
-    static __device__ __forceinline__ void store32(float* dst, const float (&v)[32], bool vec, int valid)
+    template <int W>
+    static __device__ __forceinline__ void store(float* dst, const float (&v)[W], bool vec, int valid)
     {
         if (vec) {
             float4* d = reinterpret_cast<float4*>(dst);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            for (int i = 0; i < W / 4; ++i) d[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
         } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
+            for (int i = 0; i < W; ++i)
                 if (i < valid) dst[i] = v[i];
         }
     }
 };
 
-// Tile order: groups of 16 tile-rows walk the N tiles together so that the CTAs running
-// at the same time share A and B tiles in L2.
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn)
+// Tile order: groups of `group` tile rows walk the N tiles together so that the CTAs running at
+// the same time share A and B tiles in L2 (and, with the fused all-reduce, so that whole row
+// groups of the output finish early).
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int group, int& tm, int& tn)
 {
-    constexpr int kGroup = 16;
-    const int per_group = kGroup * tiles_n;
+    const int per_group = group * tiles_n;
     const int g = tile / per_group;
-    const int first = g * kGroup;
-    const int rows = min(kGroup, tiles_m - first);
+    const int first = g * group;
+    const int rows = min(group, tiles_m - first);
     const int r = tile - g * per_group;
     tm = first + r % rows;
     tn = r / rows;
 }
 
-template <int EPI, typename OutT>
-__global__ void __launch_bounds__(kThreads, 1)
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded wait until *flag has reached `epoch` (flags only grow; signed difference tolerates wrap).
+__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t epoch, uint32_t* status, uint32_t site)
+{
+    const unsigned long long t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys_u32(flag) - epoch) < 0) {
+        if ((++spins & 0x3Fu) == 0 && ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
+            atomicCAS(status, 0u, ptx::kStatusTimeout | (site << 24) | (blockIdx.x & 0xFFFFFFu));
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc)
+{
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+__device__ __forceinline__ void multimem_st_bf16x8(__nv_bfloat16* mc, uint4 v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+// bar.sync on a named barrier shared by the reducer warps only
+__device__ __forceinline__ void reducer_barrier()
+{
+    asm volatile("bar.sync 1, %0;" ::"n"(kReducerThreads) : "memory");
+}
+
+template <int EPI, typename OutT, int BN, bool AR>
+__global__ void __launch_bounds__(kBaseThreads + (AR ? kReducerThreads : 0), 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const __grid_constant__ CUtensorMap tmB2, const Params p)
 {
+    using CF = Cfg<BN>;
+    constexpr int kStages = CF::kStages;
+    constexpr int kStageBytes = CF::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
+    __shared__ int s_abort;
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = smem_base + kStages * kStageBytes;
     // barrier layout (8 bytes each): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2], then tmem ptr
@@ -124,12 +204,14 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int lane = threadIdx.x & 31;
     const int num_kb = (p.K + kBK - 1) / kBK;
     const int num_tiles = p.tiles_m * p.tiles_n;
-    constexpr int kOutCols = (EPI == kEpiSwiGLU) ? 128 : kBN;   // output columns per tile
+    constexpr int kOutCols = (EPI == kEpiSwiGLU) ? BN / 2 : BN;   // output columns per tile
+    constexpr int kCW = (kOutCols % 32 == 0) ? 32 : 16;           // columns per TMEM load
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull_bar(b), 1); ptx::mbar_init(tempty_bar(b), 4); }
         ptx::fence_mbar_init();
+        s_abort = 0;
     }
     if (warp == 1) {
         ptx::tmem_alloc(tmem_slot, kTmemCols);
@@ -148,16 +230,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             if (EPI == kEpiSwiGLU) ptx::tma_prefetch_desc(&tmB2);
             int stage = 0; uint32_t phase = 0; bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
                 const int m0 = tm * kBM, n0 = tn * kOutCols;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, p.status, 1)) { ok = false; break; }
-                    const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
+                    const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + CF::kABytes;
                     ptx::mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
                     ptx::tma_load_2d(sa, &tmA, full_bar(stage), kb * kBK, m0);
                     if (EPI == kEpiSwiGLU) {
                         ptx::tma_load_2d(sb, &tmB, full_bar(stage), kb * kBK, n0);
-                        ptx::tma_load_2d(sb + 128 * kBK, &tmB2, full_bar(stage), kb * kBK, n0);
+                        ptx::tma_load_2d(sb + (BN / 2) * kBK, &tmB2, full_bar(stage), kb * kBK, n0);
                     } else {
                         ptx::tma_load_2d(sb, &tmB, full_bar(stage), kb * kBK, n0);
                     }
@@ -169,18 +251,18 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
         if (ptx::elect_one()) {
-            constexpr uint32_t idesc = ptx::umma_idesc(0 /*E4M3*/, 0 /*E4M3*/, kBM, kBN);
+            constexpr uint32_t idesc = ptx::umma_idesc(0 /*E4M3*/, 0 /*E4M3*/, kBM, BN);
             int stage = 0; uint32_t phase = 0; bool ok = true;
             int t = 0;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
                 const int buf = t & 1;
                 if (!ptx::mbar_wait(tempty_bar(buf), ((t >> 1) & 1u) ^ 1u, p.status, 2)) { ok = false; break; }
                 ptx::tcgen05_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buf * kBN;
+                const uint32_t d_tmem = tmem_base + buf * 256;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(full_bar(stage), phase, p.status, 3)) { ok = false; break; }
                     ptx::tcgen05_fence_after_sync();
-                    const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + kABytes;
+                    const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + CF::kABytes;
                     const uint64_t da = ptx::smem_desc_sw128_kmajor(sa), db = ptx::smem_desc_sw128_kmajor(sb);
 #pragma unroll
                     for (int k = 0; k < kBK / 32; ++k)   // 32 bytes of K per instruction: +2 in 16-byte units
@@ -192,7 +274,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
             if (!ok) __nanosleep(200000);
         }
-    } else {
+    } else if (warp < 6) {
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;                         // TMEM lane quadrant this warp may read
         OutT* Cbase = static_cast<OutT*>(p.C);
@@ -200,26 +282,26 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         int t = 0; bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
             const int buf = t & 1;
-            int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
             const int row = tm * kBM + q * 32 + lane;
             const int n0 = tn * kOutCols;
             if (!ptx::mbar_wait(tfull_bar(buf), (t >> 1) & 1u, p.status, 4)) { ok = false; break; }
             ptx::tcgen05_fence_after_sync();
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kBN;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 256;
             float rs = 1.0f;
             if (EPI != kEpiTensor) rs = (row < p.M) ? __ldg(p.row_scale + row) : 0.0f;
 #pragma unroll 1
-            for (int c = 0; c < kOutCols / 32; ++c) {
-                uint32_t r[32];
-                float v[32];
-                const int col0 = n0 + c * 32;
-                ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+            for (int c = 0; c < kOutCols / kCW; ++c) {
+                uint32_t r[kCW];
+                float v[kCW];
+                const int col0 = n0 + c * kCW;
+                ptx::tmem_ld_32x32b<kCW>(taddr + c * kCW, r);
                 if (EPI == kEpiSwiGLU) {
-                    uint32_t ru[32];
-                    ptx::tmem_ld_32x32b_x32(taddr + 128 + c * 32, ru);
+                    uint32_t ru[kCW];
+                    ptx::tmem_ld_32x32b<kCW>(taddr + BN / 2 + c * kCW, ru);
                     ptx::tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < kCW; ++i) {
                         const int col = col0 + i;
                         const float sg = (col < p.N) ? __ldg(p.col_scale + col) : 0.0f;
                         const float su = (col < p.N) ? __ldg(p.col_scale2 + col) : 0.0f;
@@ -230,7 +312,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 } else {
                     ptx::tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < kCW; ++i) {
                         float s;
                         if (EPI == kEpiTensor) s = p.alpha;
                         else { const int col = col0 + i; s = rs * ((col < p.N) ? __ldg(p.col_scale + col) : 0.0f); }
@@ -238,14 +320,78 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     }
                 }
                 if (row < p.M && col0 < p.N) {
-                    const int valid = min(32, p.N - col0);
-                    OutPack<OutT>::store32(Cbase + (long long)row * p.ldc + col0, v, ld_ok && valid == 32, valid);
+                    const int valid = min(kCW, p.N - col0);
+                    OutPack<OutT>::template store<kCW>(Cbase + (long long)row * p.ldc + col0, v, ld_ok && valid == kCW, valid);
                 }
             }
             // accumulator drained: hand the TMEM buffer back to the MMA warp
             ptx::tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+            if (AR) {
+                // this warp's share of the tile is in memory: count it; the warp that completes
+                // the group tells every rank
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) {
+                    const int g = tm / p.group;
+                    const uint32_t target = 4u * min(p.group, p.tiles_m - g * p.group) * p.tiles_n;
+                    if (atomicAdd(p.counters + g, 1u) + 1u == target) {
+                        __threadfence_system();
+                        for (int r = 0; r < p.world; ++r)
+                            st_release_sys_u32(p.flag_ptrs[r] + p.flag_offset_words + g * kMaxWorld + p.rank, p.epoch);
+                    }
+                }
+            }
+        }
+    } else if (AR) {
+        // ---------------------------------------------------------------- reducers
+        const int rt = threadIdx.x - kBaseThreads;
+        const int groups = (p.tiles_m + p.group - 1) / p.group;
+        const uint32_t* my_flags = p.flag_ptrs[p.rank] + p.flag_offset_words;
+        bool ok = true;
+        for (int g = 0; g < groups && ok; ++g) {
+            if (rt < p.world && !wait_flag_sys(my_flags + g * kMaxWorld + rt, p.epoch, p.status, 5)) s_abort = 1;
+            reducer_barrier();
+            if (*reinterpret_cast<volatile int*>(&s_abort)) { ok = false; break; }
+            const long long row0 = static_cast<long long>(g) * p.group * kBM;
+            const long long rows = min(static_cast<long long>(p.group) * kBM, static_cast<long long>(p.M) - row0);
+            const long long vecs = rows * p.N / 8;                  // 8 fp32 -> 8 bf16 (16 bytes)
+            const long long v0 = vecs * p.rank / p.world, v1 = vecs * (p.rank + 1) / p.world;
+            const long long base = row0 * p.N;
+            for (long long v = v0 + blockIdx.x * static_cast<long long>(kReducerThreads) + rt; v < v1;
+                 v += static_cast<long long>(gridDim.x) * kReducerThreads) {
+                const long long e = base + v * 8;
+                float4 a, b;
+                if (p.partial_mc != nullptr) {
+                    a = multimem_ld_reduce_f32x4(p.partial_mc + e);
+                    b = multimem_ld_reduce_f32x4(p.partial_mc + e + 4);
+                } else {
+                    a = make_float4(0.f, 0.f, 0.f, 0.f); b = a;
+                    for (int r = 0; r < p.world; ++r) {             // fixed rank order
+                        const float4* src = reinterpret_cast<const float4*>(p.partial_ptrs[r] + e);
+                        const float4 x = __ldcg(src), y = __ldcg(src + 1);
+                        a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+                        b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+                    }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
+                o.z = pack_bf16x2(b.x, b.y); o.w = pack_bf16x2(b.z, b.w);
+                if (p.out_mc != nullptr) multimem_st_bf16x8(p.out_mc + e, o);
+                else for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.out_ptrs[r] + e) = o;
+            }
+        }
+        // every rank's broadcasts into this rank's output must have landed before the kernel ends
+        reducer_barrier();
+        if (ok) {
+            if (rt == 0) {
+                __threadfence_system();
+                if (atomicAdd(p.counters + kMaxGroups, 1u) + 1u == gridDim.x)
+                    for (int r = 0; r < p.world; ++r)
+                        st_release_sys_u32(p.flag_ptrs[r] + p.flag_offset_words + kMaxGroups * kMaxWorld + p.rank, p.epoch);
+            }
+            if (rt < p.world) wait_flag_sys(my_flags + kMaxGroups * kMaxWorld + rt, p.epoch, p.status, 6);
         }
     }
 

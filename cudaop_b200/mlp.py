@@ -13,11 +13,12 @@ Per rank and forward pass:
   2. gate/up GEMM + SwiGLU, fused epilogue -> H  (bf16) [T, I/R]       [b200q_gemm_fp8_swiglu]
   3. quantise H per token                  -> Hq (E4M3), sh            [b200q_quant_rows_e4m3]
   4. down GEMM, per-token x per-channel    -> partial Y                [b200q_gemm_fp8_rowcol]
-  5. R > 1: sum all-reduce of the fp32 partials, in token chunks on a side stream so that it
-     overlaps the next chunk's steps 2-4.  Default: the library's own NVSwitch kernel
-     (b200q_allreduce_f32_to_bf16: multimem.ld_reduce in the switch, one rounding to bf16,
-     multimem.st broadcast) over torch symmetric memory; ``comm="nccl"`` uses
-     torch.distributed.all_reduce + a cast instead.
+  5. R > 1: sum all-reduce of the fp32 partials.  ``comm="fused"`` (default): step 4 and the
+     all-reduce are ONE kernel (b200q_gemm_fp8_rowcol_allreduce) — finished row groups are summed
+     in the NVSwitch (multimem.ld_reduce), rounded once to bf16 and broadcast (multimem.st) while
+     later groups are still being multiplied.  ``comm="symm"``: the stand-alone NVSwitch kernel
+     (b200q_allreduce_f32_to_bf16) per token chunk on a side stream; ``comm="nccl"``:
+     torch.distributed.all_reduce + a cast.  All three keep fp32 accumulation and identical replicas.
 """
 from __future__ import annotations
 
@@ -77,14 +78,16 @@ class TensorParallelMLP:
         self._epoch = 0
         if world > 1:
             self.comm = comm
-            if comm in ("auto", "symm"):
+            if comm in ("auto", "fused", "symm"):
                 try:
                     self._init_symmetric(T, H)
-                    self.comm = "symm"
+                    self.comm = "symm" if comm == "symm" else "fused"
                 except Exception:
-                    if comm == "symm":
+                    if comm != "auto":
                         raise
                     self.comm = "nccl"
+            if self.comm == "fused":
+                self.chunks = 1
             if self.comm == "nccl":
                 self.partial = torch.empty((T, H), dtype=torch.float32, device=dev)
         self.kernel_launches_per_forward = 0
@@ -99,7 +102,9 @@ class TensorParallelMLP:
         dev = self.device
         self.partial = symm.empty((T, H), dtype=torch.float32, device=dev)
         self.y_sym = symm.empty((T, H), dtype=torch.bfloat16, device=dev)
-        nflags = ops.lib().b200q_allreduce_signal_bytes() // 4
+        self._fused_flag_offset = ops.lib().b200q_allreduce_signal_bytes()
+        nflags = (self._fused_flag_offset + ops.lib().b200q_fused_allreduce_flag_bytes()) // 4
+        self._counters = torch.zeros((ops.lib().b200q_fused_allreduce_counter_bytes() // 4,), dtype=torch.int32, device=dev)
         self.flags = symm.empty((nflags,), dtype=torch.int32, device=dev)
         self.flags.zero_()
         self._hp = symm.rendezvous(self.partial, group)
@@ -140,6 +145,17 @@ class TensorParallelMLP:
         if self.world == 1:
             ops._raise(L.b200q_gemm_fp8_rowcol(hq.data_ptr(), self.wd.data_ptr(), y[lo:hi].data_ptr(), n, H, Il,
                                                shs.data_ptr(), self.sd.data_ptr(), 0, st), "down")
+        elif self.comm == "fused":
+            if lo != 0:
+                raise ValueError("the fused all-reduce covers the whole token range in one call")
+            self._epoch += 1
+            mc_p = self._hp.multicast_ptr if self.multicast else None
+            mc_y = self._hy.multicast_ptr if self.multicast else None
+            ops._raise(L.b200q_gemm_fp8_rowcol_allreduce(
+                hq.data_ptr(), self.wd.data_ptr(), self.partial.data_ptr(), n, H, Il, shs.data_ptr(), self.sd.data_ptr(),
+                self._hp.buffer_ptrs_dev, self._hy.buffer_ptrs_dev, self._hf.buffer_ptrs_dev, mc_p, mc_y,
+                self._counters.data_ptr(), self._fused_flag_offset, self._epoch, self.rank, self.world, st),
+                "down + all-reduce")
         else:
             ops._raise(L.b200q_gemm_fp8_rowcol(hq.data_ptr(), self.wd.data_ptr(), self.partial[lo:hi].data_ptr(),
                                                n, H, Il, shs.data_ptr(), self.sd.data_ptr(), 1, st), "down")
@@ -150,14 +166,17 @@ class TensorParallelMLP:
         T, H = x.shape
         if H != self.hidden or T > self.max_tokens:
             raise ValueError(f"x must be [<= {self.max_tokens}, {self.hidden}]")
-        if self.comm == "symm":
+        if self.comm in ("symm", "fused"):
             y = self.y_sym[:T]
         else:
             y = out if out is not None else torch.empty((T, H), dtype=torch.bfloat16, device=x.device)
         launches = 0
         with torch.cuda.device(self.device):
-            if self.world == 1:
+            if self.world == 1 or self.comm == "fused":
                 launches += self._stage(x, y, 0, T)
+                if out is not None and self.comm == "fused":
+                    out[:T].copy_(y)
+                    y = out
             else:
                 import torch.distributed as dist
                 main = torch.cuda.current_stream()

@@ -83,6 +83,7 @@ int b200q_gemm_sp24_fp8(const void* Acomp, const void* Ameta, const void* B, voi
                         float scale_a, float scale_b, void* stream);
 
 /* Tuning knobs (process-wide): width of the B tile, 128 / 192 / 256 columns. */
+int b200q_fp8_set_tile_n(int bn);      /* 0 = chosen per problem (default), 224 or 256 */
 int b200q_nvfp4_set_tile_n(int bn);
 int b200q_sp24_set_tile_n(int bn);
 
@@ -105,6 +106,23 @@ int b200q_allreduce_f32_to_bf16(const void* const* partial_ptrs_dev, void* const
                                 long long elem_offset, long long elems, int rank, int world, unsigned int epoch,
                                 unsigned int signal_offset_bytes, int ctas, void* stream);
 size_t b200q_allreduce_signal_bytes(void);
+
+/* The MLP's row-parallel down projection with the all-reduce fused into the same kernel (one
+ * kernel in place of GEMM -> ncclAllReduce, op/nccl/nccl_mlp_test.cu:170-195): every rank calls it
+ * at the same time; the kernel writes fp32 partial tiles to `partial_local` (this rank's entry of
+ * partial_ptrs_dev), and while later row groups are still being multiplied its reducer warps sum
+ * finished groups across ranks through NVSwitch and broadcast the bf16 result to every rank's
+ * output.  Pointer-array, multicast, epoch and flag arguments as for b200q_allreduce_f32_to_bf16;
+ * the flag buffer needs b200q_fused_allreduce_flag_bytes() bytes from flag_offset_bytes on (zeroed
+ * once), `counters_local` is b200q_fused_allreduce_counter_bytes() of this rank's own memory. */
+int b200q_gemm_fp8_rowcol_allreduce(const void* A, const void* B, void* partial_local, int M, int N, int K,
+                                    const float* row_scale, const float* col_scale,
+                                    const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                    void* const* flag_ptrs_dev, const void* partial_multicast, void* out_multicast,
+                                    void* counters_local, unsigned int flag_offset_bytes, unsigned int epoch, int rank,
+                                    int world, void* stream);
+size_t b200q_fused_allreduce_flag_bytes(void);
+size_t b200q_fused_allreduce_counter_bytes(void);
 
 /* Reads (and optionally clears) the device status word of the current device into *host_out.
  * 0 = no kernel of this library gave up on a bounded wait.  Synchronises the device. */

@@ -22,11 +22,12 @@ def _worker(rank, world, port, mode, out_dir):
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-    T, H, I = 256, 512, 1024
+    T, H, I = 1200, 512, 1024           # 10 tile rows: three row groups in the fused kernel, ragged last
     case = oracle.make_mlp_case(T, H, I, seed=31)
     ts = [torch.from_numpy(np.ascontiguousarray(t)) for t in case[1:]]
-    mlp = TensorParallelMLP(*ts, rank=rank, world=world, max_tokens=T, chunks=2, comm="symm" if mode != "nccl" else "nccl")
-    if mode == "p2p":
+    comm = {"multicast": "symm", "p2p": "symm", "nccl": "nccl", "fused": "fused", "fused_p2p": "fused"}[mode]
+    mlp = TensorParallelMLP(*ts, rank=rank, world=world, max_tokens=T, chunks=2, comm=comm)
+    if mode in ("p2p", "fused_p2p"):
         mlp.multicast = False
     x = torch.from_numpy(case[0].view(np.int16)).cuda().view(torch.bfloat16)
     y = mlp(x).clone()
@@ -35,19 +36,22 @@ def _worker(rank, world, port, mode, out_dir):
     assert ops.status() == 0
     assert torch.equal(y, y2)
     # the kernel's sum against the fp32 partials of both ranks gathered with NCCL
-    parts = [torch.empty_like(mlp.partial) for _ in range(world)]
-    dist.all_gather(parts, mlp.partial.contiguous())
-    want = sum(p for p in parts).to(torch.bfloat16)
+    if mode == "nccl":
+        want = mlp.partial.to(torch.bfloat16)          # NCCL reduced the partials in place
+    else:
+        parts = [torch.empty_like(mlp.partial) for _ in range(world)]
+        dist.all_gather(parts, mlp.partial.contiguous())
+        want = sum(p for p in parts).to(torch.bfloat16)
     torch.save({"y": y.cpu(), "want": want.cpu(), "comm": mlp.comm, "mc": getattr(mlp, "multicast", None)},
                os.path.join(out_dir, f"{mode}_r{rank}.pt"))
     dist.barrier(); dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("mode", ["multicast", "p2p", "nccl"])
+@pytest.mark.parametrize("mode", ["fused", "fused_p2p", "multicast", "p2p", "nccl"])
 def test_two_rank_mlp_allreduce(mode, tmp_path):
     _need_two()
     import torch.multiprocessing as mp
-    port = 29600 + (os.getpid() % 1000) + {"multicast": 0, "p2p": 1, "nccl": 2}[mode]
+    port = 29600 + (os.getpid() % 1000) + {"multicast": 0, "p2p": 1, "nccl": 2, "fused": 3, "fused_p2p": 4}[mode]
     mp.spawn(_worker, args=(2, port, mode, str(tmp_path)), nprocs=2, join=True)
     r0 = torch.load(tmp_path / f"{mode}_r0.pt"); r1 = torch.load(tmp_path / f"{mode}_r1.pt")
     print(mode, "comm:", r0["comm"], "multicast:", r0["mc"])
