@@ -273,7 +273,8 @@ def run_ours(args):
     sg = rand_scale(loc, 4000 + rank); su = rand_scale(loc, 5000 + rank); sd = rand_scale(HIDDEN, 6000)
     mlp = TensorParallelMLP(wg, sg, wu, su, wd, sd, rank=rank, world=world, device=dev, max_tokens=TOKENS,
                             chunks=args.chunks if world > 1 else 1, presharded=True, comm=args.comm,
-                            ar_ctas=args.ar_ctas)
+                            ar_ctas=args.ar_ctas, use_multicast=args.multicast,
+                            partial_dtype=torch.float32 if args.partial == "fp32" else torch.bfloat16)
     del wg, wu, wd
 
     gen.manual_seed(7)
@@ -315,6 +316,14 @@ def run_ours(args):
     torch.cuda.synchronize()
     top_ms = [a.elapsed_time(b) for a, b in evs[-args.steps * max(1, mlp.chunks if world > 1 else 1):]]
     launches = mlp.kernel_launches_per_forward * args.steps
+    # ---- one more pass with events around every kernel (not part of the timed region)
+    mlp.stage_events = []
+    for _ in range(3):
+        mlp.forward(x)
+    torch.cuda.synchronize()
+    names = ("quant_x", "gate_up_swiglu", "quant_h", "down_allreduce" if world > 1 else "down")
+    kernels_ms = {n: min(m[i].elapsed_time(m[i + 1]) for m in mlp.stage_events) for i, n in enumerate(names)}
+    mlp.stage_events = None
     # ---- end to end: pinned host input -> device, forward, result back to pinned host memory
     def e2e_step():
         x.copy_(x_host, non_blocking=True)
@@ -338,12 +347,13 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 acc -> bf16",
         "data": "synthetic", "config": dict(workload_config(world), comm=mlp.comm,
-                                             multicast=getattr(mlp, "multicast", None), chunks=mlp.chunks),
+                                             multicast=getattr(mlp, "multicast", None), chunks=mlp.chunks,
+                                             partial_dtype=str(mlp.partial_dtype).replace("torch.", "")),
         "tflops": MLP_FLOPS / (ms_step * 1e-3) / 1e12,
         "clocks": clocks,
         "e2e": {"value": TOKENS / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": TOKENS * HIDDEN * 2, "d2h_bytes_per_step": TOKENS * HIDDEN * 2},
-        "gpu_launches": launches,
+        "gpu_launches": launches, "kernels_ms": kernels_ms,
         "roofline": {"bound": "tensor", "kernel": "gemm_fp8_kernel<SwiGLU> (gate/up projection)",
                      "achieved": top_tf, "peak": peak, "unit": "TFLOP/s", "frac": top_tf / peak,
                      "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} (FP8 runs at twice the bf16 "
@@ -380,7 +390,9 @@ def main():
     ap.add_argument("--chunks", type=int, default=4, help="token chunks for all-reduce overlap (N > 1)")
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "symm", "nccl"],
                     help="all-reduce: the library's NVSwitch kernel over symmetric memory, or NCCL")
-    ap.add_argument("--ar-ctas", type=int, default=32)
+    ap.add_argument("--ar-ctas", type=int, default=64)
+    ap.add_argument("--partial", default="bf16", choices=["bf16", "fp32"], help="dtype of the partial outputs that cross NVLink")
+    ap.add_argument("--multicast", action="store_true", help="reduce and broadcast in the NVSwitch (multimem) instead of peer loads/stores")
     ap.add_argument("--cpu-tokens", type=int, default=64, help="tokens in the CPU-baseline sample")
     ap.add_argument("--no-cases", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

@@ -16,13 +16,14 @@
 // on a timeout the kernel records it in the status word and returns.
 #include "common.cuh"
 #include "ptx.cuh"
+#include "ar_common.cuh"
 #include "../../include/b200q.h"
 
 namespace b200q {
 namespace ar {
 
 constexpr int kThreads = 512;
-constexpr int kMaxWorld = 16;
+constexpr int kMaxWorld = arc::kMaxWorld;
 constexpr int kMaxCtas = 128;
 
 struct Params {
@@ -38,16 +39,8 @@ struct Params {
     uint32_t* status;
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
-{
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
-{
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
+using arc::st_release_sys;
+using arc::ld_acquire_sys;
 
 // Barrier between the CTAs with the same index on every rank.  Flags: pad[phase][cta][src_rank].
 // Returns false if a peer did not arrive within the wait limit.
@@ -76,59 +69,35 @@ __device__ __forceinline__ bool rank_barrier(const Params& p, int phase, bool& o
     return __syncthreads_and(ok);
 }
 
-__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc)
-{
-    float4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "l"(mc)
-                 : "memory");
-    return v;
-}
-__device__ __forceinline__ void multimem_st_bf16x8(__nv_bfloat16* mc, uint4 v)
-{
-    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
-                 ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
-                 : "memory");
-}
-
-template <bool MC>
+template <bool MC, bool PartialBf16, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
-allreduce_f32_to_bf16_kernel(const Params p)
+allreduce_to_bf16_kernel(const Params p)
 {
     bool dummy = true;
     if (!rank_barrier(p, 0, dummy)) return;
 
     const long long per = p.elems / p.world;                 // elements this rank reduces
     const long long base = p.offset + per * p.rank;
-    const long long vecs = per / 8;                           // 8 fp32 in -> 8 bf16 (16 bytes) out
-    for (long long v = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; v < vecs;
-         v += static_cast<long long>(gridDim.x) * kThreads) {
-        const long long e = base + v * 8;
-        float4 a, b;
-        if (MC) {
-            a = multimem_ld_reduce_f32x4(p.partial_mc + e);
-            b = multimem_ld_reduce_f32x4(p.partial_mc + e + 4);
-        } else {
-            a = make_float4(0.f, 0.f, 0.f, 0.f); b = a;
-            for (int r = 0; r < p.world; ++r) {               // fixed rank order
-                const float4* src = reinterpret_cast<const float4*>(p.partial_ptrs[r] + e);
-                const float4 x = __ldcg(src), y = __ldcg(src + 1);
-                a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
-                b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+    const long long vecs = per / 8;                           // 8 values in -> 8 bf16 (16 bytes) out
+    const long long stride = static_cast<long long>(gridDim.x) * kThreads;
+    for (long long vb = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; vb < vecs; vb += stride * UNROLL) {
+        uint4 o[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+            if (vb + u * stride < vecs)
+                o[u] = arc::reduce8<MC, PartialBf16>(reinterpret_cast<const void* const*>(p.partial_ptrs), p.partial_mc, p.world,
+                                                     base + (vb + u * stride) * 8);
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u)
+            if (vb + u * stride < vecs) {
+                const long long e = base + (vb + u * stride) * 8;
+                arc::broadcast8<MC>(p.out_ptrs, p.out_mc, p.world, e, o[u]);
             }
-        }
-        uint4 o;
-        o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
-        o.z = pack_bf16x2(b.x, b.y); o.w = pack_bf16x2(b.z, b.w);
-        if (MC) {
-            multimem_st_bf16x8(p.out_mc + e, o);
-        } else {
-            for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.out_ptrs[r] + e) = o;
-        }
     }
     rank_barrier(p, 1, dummy);
 }
+
+int g_unroll = 4;
 
 }  // namespace ar
 }  // namespace b200q
@@ -140,10 +109,10 @@ size_t b200q_allreduce_signal_bytes(void)
     return static_cast<size_t>(2) * b200q::ar::kMaxCtas * b200q::ar::kMaxWorld * sizeof(uint32_t);
 }
 
-int b200q_allreduce_f32_to_bf16(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
-                                void* const* signal_ptrs_dev, const void* partial_multicast, void* out_multicast,
-                                long long elem_offset, long long elems, int rank, int world, unsigned int epoch,
-                                unsigned int signal_offset_bytes, int ctas, void* stream)
+int b200q_allreduce_to_bf16(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                            void* const* signal_ptrs_dev, const void* partial_multicast, void* out_multicast,
+                            int partial_is_bf16, long long elem_offset, long long elems, int rank, int world,
+                            unsigned int epoch, unsigned int signal_offset_bytes, int ctas, void* stream)
 {
     using namespace b200q;
     if (partial_ptrs_dev == nullptr || out_ptrs_dev == nullptr || signal_ptrs_dev == nullptr) return cudaErrorInvalidValue;
@@ -162,9 +131,21 @@ int b200q_allreduce_f32_to_bf16(const void* const* partial_ptrs_dev, void* const
     p.status = status_ptr();
     if (p.status == nullptr) return cudaErrorInvalidDevice;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (partial_multicast != nullptr) ar::allreduce_f32_to_bf16_kernel<true><<<ctas, ar::kThreads, 0, s>>>(p);
-    else ar::allreduce_f32_to_bf16_kernel<false><<<ctas, ar::kThreads, 0, s>>>(p);
+    const bool mc = partial_multicast != nullptr;
+#define B200Q_AR(MC_, BF_, U_) ar::allreduce_to_bf16_kernel<MC_, BF_, U_><<<ctas, ar::kThreads, 0, s>>>(p)
+#define B200Q_AR_U(MC_, BF_) do { if (ar::g_unroll >= 8) B200Q_AR(MC_, BF_, 8); else if (ar::g_unroll >= 4) B200Q_AR(MC_, BF_, 4); else if (ar::g_unroll >= 2) B200Q_AR(MC_, BF_, 2); else B200Q_AR(MC_, BF_, 1); } while (0)
+    if (partial_is_bf16) { if (mc) B200Q_AR_U(true, true); else B200Q_AR_U(false, true); }
+    else { if (mc) B200Q_AR_U(true, false); else B200Q_AR_U(false, false); }
+#undef B200Q_AR_U
+#undef B200Q_AR
     return cudaGetLastError();
+}
+
+int b200q_allreduce_set_unroll(int unroll)
+{
+    if (unroll < 1 || unroll > 8) return cudaErrorInvalidValue;
+    b200q::ar::g_unroll = unroll;
+    return 0;
 }
 
 }  // extern "C"

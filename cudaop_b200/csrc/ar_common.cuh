@@ -1,0 +1,103 @@
+// Device helpers shared by the stand-alone all-reduce kernel and the GEMM with the all-reduce
+// fused in: system-scope flags with bounded waits, NVSwitch multimem loads/stores, and the
+// cross-rank sum of eight partial values.
+#pragma once
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200q {
+namespace arc {
+
+constexpr int kMaxWorld = 16;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded wait until *flag has reached `epoch` (flags only grow; the signed difference tolerates
+// wrap-around).  On a timeout records (site, block) in *status and returns false.
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* status, uint32_t site)
+{
+    const unsigned long long t0 = ptx::globaltimer_ns();
+    uint32_t spins = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) < 0) {
+        if ((++spins & 0x3Fu) == 0 && ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
+            atomicCAS(status, 0u, ptx::kStatusTimeout | (site << 24) | (blockIdx.x & 0xFFFFFFu));
+            return false;
+        }
+    }
+    return true;
+}
+
+// multimem.ld_reduce.add.v4.f32: the switch adds the same 16 bytes of every rank's buffer
+__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc)
+{
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+// multimem.ld_reduce.add.acc::f32.v4.bf16x2: eight bf16 per rank added in the switch
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const __nv_bfloat16* mc)
+{
+    uint4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+// multimem.st.v4.bf16x2: one 16-byte store delivered to every rank's buffer
+__device__ __forceinline__ void multimem_st_bf16x8(__nv_bfloat16* mc, uint4 v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Sum over ranks of eight consecutive partial values starting at element e, returned as eight
+// bf16 (one round-to-nearest-even of the fp32 sum).  MC: additions in the switch (their order and
+// the rounding of the bf16 form are the hardware's); otherwise plain peer loads added in rank order.
+template <bool MC, bool PartialBf16>
+__device__ __forceinline__ uint4 reduce8(const void* const* partial_ptrs, const void* partial_mc, int world, long long e)
+{
+    if (PartialBf16) {
+        if (MC) return multimem_ld_reduce_bf16x8(static_cast<const __nv_bfloat16*>(partial_mc) + e);
+        float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int r = 0; r < world; ++r) {
+            const uint4 x = __ldcg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(partial_ptrs[r]) + e));
+            const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { acc[2 * i] += __uint_as_float(w[i] << 16); acc[2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u); }
+        }
+        return make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]), pack_bf16x2(acc[4], acc[5]),
+                          pack_bf16x2(acc[6], acc[7]));
+    }
+    float4 a, b;
+    if (MC) {
+        a = multimem_ld_reduce_f32x4(static_cast<const float*>(partial_mc) + e);
+        b = multimem_ld_reduce_f32x4(static_cast<const float*>(partial_mc) + e + 4);
+    } else {
+        a = make_float4(0.f, 0.f, 0.f, 0.f); b = a;
+        for (int r = 0; r < world; ++r) {
+            const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(partial_ptrs[r]) + e);
+            const float4 x = __ldcg(src), y = __ldcg(src + 1);
+            a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+            b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+        }
+    }
+    return make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
+}
+
+template <bool MC>
+__device__ __forceinline__ void broadcast8(__nv_bfloat16* const* out_ptrs, __nv_bfloat16* out_mc, int world, long long e, uint4 o)
+{
+    if (MC) multimem_st_bf16x8(out_mc + e, o);
+    else for (int r = 0; r < world; ++r) *reinterpret_cast<uint4*>(out_ptrs[r] + e) = o;
+}
+
+}  // namespace arc
+}  // namespace b200q

@@ -89,17 +89,17 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
     p.status = status_ptr();
     if (p.status == nullptr) return cudaErrorInvalidDevice;
     if (ar) {
-        if (epi != kEpiRowCol || !out_f32 || N % 8 != 0 || ldc != N || !aligned16(C)) return cudaErrorInvalidValue;
+        if (epi != kEpiRowCol || N % 8 != 0 || ldc != N || !aligned16(C)) return cudaErrorInvalidValue;
         if (ar->partial_ptrs == nullptr || ar->out_ptrs == nullptr || ar->flag_ptrs == nullptr || ar->counters == nullptr)
             return cudaErrorInvalidValue;
         if (ar->world < 1 || ar->world > kMaxWorld || ar->rank < 0 || ar->rank >= ar->world) return cudaErrorInvalidValue;
         if ((ar->partial_mc == nullptr) != (ar->out_mc == nullptr) || ar->flag_offset_bytes % 4 != 0) return cudaErrorInvalidValue;
         p.group = 4;                                   // 512-row groups finish (and are reduced) early
         if ((p.tiles_m + p.group - 1) / p.group > kMaxGroups) return cudaErrorInvalidValue;
-        p.partial_ptrs = reinterpret_cast<const float* const*>(ar->partial_ptrs);
+        p.partial_ptrs = ar->partial_ptrs;
         p.out_ptrs = reinterpret_cast<__nv_bfloat16* const*>(ar->out_ptrs);
         p.flag_ptrs = reinterpret_cast<uint32_t* const*>(ar->flag_ptrs);
-        p.partial_mc = static_cast<const float*>(ar->partial_mc);
+        p.partial_mc = ar->partial_mc;
         p.out_mc = static_cast<__nv_bfloat16*>(ar->out_mc);
         p.counters = static_cast<uint32_t*>(ar->counters);
         p.flag_offset_words = ar->flag_offset_bytes / 4; p.epoch = ar->epoch; p.rank = ar->rank; p.world = ar->world;
@@ -117,7 +117,8 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
 
 #define B200Q_LAUNCH(EPI, T, AR_) \
     (bn == 224 ? launch<EPI, T, 224, AR_>(tmA, tmB, tmB2, p, stream) : launch<EPI, T, 256, AR_>(tmA, tmB, tmB2, p, stream))
-    if (ar) return launch<kEpiRowCol, float, 256, true>(tmA, tmB, tmB2, p, stream);
+    if (ar) return out_f32 ? launch<kEpiRowCol, float, 256, true>(tmA, tmB, tmB2, p, stream)
+                           : launch<kEpiRowCol, __nv_bfloat16, 256, true>(tmA, tmB, tmB2, p, stream);
     switch (epi) {
     case kEpiTensor: return out_f32 ? B200Q_LAUNCH(kEpiTensor, float, false) : B200Q_LAUNCH(kEpiTensor, __nv_bfloat16, false);
     case kEpiRowCol: return out_f32 ? B200Q_LAUNCH(kEpiRowCol, float, false) : B200Q_LAUNCH(kEpiRowCol, __nv_bfloat16, false);
@@ -159,12 +160,12 @@ int b200q_gemm_fp8_rowcol_allreduce(const void* A, const void* B, void* partial_
                                     const float* row_scale, const float* col_scale,
                                     const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
                                     void* const* flag_ptrs_dev, const void* partial_multicast, void* out_multicast,
-                                    void* counters_local, unsigned int flag_offset_bytes, unsigned int epoch, int rank,
-                                    int world, void* stream)
+                                    int partial_is_bf16, void* counters_local, unsigned int flag_offset_bytes,
+                                    unsigned int epoch, int rank, int world, void* stream)
 {
     b200q::fp8::ArArgs ar{partial_ptrs_dev, out_ptrs_dev, flag_ptrs_dev, partial_multicast, out_multicast,
                           counters_local, flag_offset_bytes, epoch, rank, world};
-    return b200q::fp8::gemm(A, B, partial_local, M, N, K, b200q::fp8::kEpiRowCol, 1, 1.0f, row_scale, col_scale,
+    return b200q::fp8::gemm(A, B, partial_local, M, N, K, b200q::fp8::kEpiRowCol, partial_is_bf16 ? 0 : 1, 1.0f, row_scale, col_scale,
                             nullptr, nullptr, N, &ar, static_cast<cudaStream_t>(stream));
 }
 

@@ -28,6 +28,7 @@
 #pragma once
 #include "common.cuh"
 #include "ptx.cuh"
+#include "ar_common.cuh"
 
 namespace b200q {
 namespace fp8 {
@@ -37,7 +38,7 @@ constexpr int kBK = 128;           // bytes == elements for FP8: one 128-byte sw
 constexpr int kBaseThreads = 192;
 constexpr int kReducerThreads = 128;
 constexpr uint32_t kTmemCols = 512;
-constexpr int kMaxWorld = 16;
+constexpr int kMaxWorld = arc::kMaxWorld;
 constexpr int kMaxGroups = 64;     // tile-row groups tracked by the fused all-reduce
 
 template <int BN>
@@ -68,10 +69,10 @@ struct Params {
     int group;                   // tile rows that walk the N tiles together
     uint32_t* status;
     // fused all-reduce (AR kernels only)
-    const float* const* partial_ptrs;    // device array [world]: every rank's fp32 partial buffer (C is this rank's)
+    const void* const* partial_ptrs;     // device array [world]: every rank's partial buffer (C is this rank's)
     __nv_bfloat16* const* out_ptrs;      // device array [world]: every rank's bf16 output
     uint32_t* const* flag_ptrs;          // device array [world]: every rank's flag buffer
-    const float* partial_mc;             // multicast address of the partial buffers, or nullptr
+    const void* partial_mc;              // multicast address of the partial buffers, or nullptr
     __nv_bfloat16* out_mc;               // multicast address of the outputs, or nullptr
     uint32_t* counters;                  // local, zeroed before the launch: [kMaxGroups + 1]
     uint32_t flag_offset_words;
@@ -132,47 +133,6 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tn = r / rows;
 }
 
-__device__ __forceinline__ void st_release_sys_u32(uint32_t* p, uint32_t v)
-{
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p)
-{
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p)
-{
-    uint32_t v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-// Bounded wait until *flag has reached `epoch` (flags only grow; signed difference tolerates wrap).
-__device__ __forceinline__ bool wait_flag_sys(const uint32_t* flag, uint32_t epoch, uint32_t* status, uint32_t site)
-{
-    const unsigned long long t0 = ptx::globaltimer_ns();
-    uint32_t spins = 0;
-    while (static_cast<int32_t>(ld_acquire_sys_u32(flag) - epoch) < 0) {
-        if ((++spins & 0x3Fu) == 0 && ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
-            atomicCAS(status, 0u, ptx::kStatusTimeout | (site << 24) | (blockIdx.x & 0xFFFFFFu));
-            return false;
-        }
-    }
-    return true;
-}
-__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc)
-{
-    float4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
-    return v;
-}
-__device__ __forceinline__ void multimem_st_bf16x8(__nv_bfloat16* mc, uint4 v)
-{
-    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
-                 ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 // bar.sync on a named barrier shared by the reducer warps only
 __device__ __forceinline__ void reducer_barrier()
 {
@@ -339,7 +299,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     if (atomicAdd(p.counters + g, 1u) + 1u == target) {
                         __threadfence_system();
                         for (int r = 0; r < p.world; ++r)
-                            st_release_sys_u32(p.flag_ptrs[r] + p.flag_offset_words + g * kMaxWorld + p.rank, p.epoch);
+                            arc::st_release_sys(p.flag_ptrs[r] + p.flag_offset_words + g * kMaxWorld + p.rank, p.epoch);
                     }
                 }
             }
@@ -351,7 +311,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const uint32_t* my_flags = p.flag_ptrs[p.rank] + p.flag_offset_words;
         bool ok = true;
         for (int g = 0; g < groups && ok; ++g) {
-            if (rt < p.world && !wait_flag_sys(my_flags + g * kMaxWorld + rt, p.epoch, p.status, 5)) s_abort = 1;
+            if (rt < p.world && !arc::wait_flag(my_flags + g * kMaxWorld + rt, p.epoch, p.status, 5)) s_abort = 1;
             reducer_barrier();
             if (*reinterpret_cast<volatile int*>(&s_abort)) { ok = false; break; }
             const long long row0 = static_cast<long long>(g) * p.group * kBM;
@@ -359,27 +319,30 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const long long vecs = rows * p.N / 8;                  // 8 fp32 -> 8 bf16 (16 bytes)
             const long long v0 = vecs * p.rank / p.world, v1 = vecs * (p.rank + 1) / p.world;
             const long long base = row0 * p.N;
-            for (long long v = v0 + blockIdx.x * static_cast<long long>(kReducerThreads) + rt; v < v1;
-                 v += static_cast<long long>(gridDim.x) * kReducerThreads) {
-                const long long e = base + v * 8;
-                float4 a, b;
-                if (p.partial_mc != nullptr) {
-                    a = multimem_ld_reduce_f32x4(p.partial_mc + e);
-                    b = multimem_ld_reduce_f32x4(p.partial_mc + e + 4);
-                } else {
-                    a = make_float4(0.f, 0.f, 0.f, 0.f); b = a;
-                    for (int r = 0; r < p.world; ++r) {             // fixed rank order
-                        const float4* src = reinterpret_cast<const float4*>(p.partial_ptrs[r] + e);
-                        const float4 x = __ldcg(src), y = __ldcg(src + 1);
-                        a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
-                        b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+            // kUnroll independent 32-byte reductions in flight per thread: the round trip through the
+            // switch is microseconds, so throughput comes from the number of loads outstanding
+            constexpr int kUnroll = 4;
+            const long long stride = static_cast<long long>(gridDim.x) * kReducerThreads;
+            for (long long vb = v0 + blockIdx.x * static_cast<long long>(kReducerThreads) + rt; vb < v1;
+                 vb += stride * kUnroll) {
+                uint4 o[kUnroll];
+                constexpr bool kBf = sizeof(OutT) == 2;          // partial tiles are stored as OutT
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const long long v = vb + u * stride;
+                    if (v < v1) {
+                        if (p.partial_mc != nullptr) o[u] = arc::reduce8<true, kBf>(p.partial_ptrs, p.partial_mc, p.world, base + v * 8);
+                        else o[u] = arc::reduce8<false, kBf>(p.partial_ptrs, p.partial_mc, p.world, base + v * 8);
                     }
                 }
-                uint4 o;
-                o.x = pack_bf16x2(a.x, a.y); o.y = pack_bf16x2(a.z, a.w);
-                o.z = pack_bf16x2(b.x, b.y); o.w = pack_bf16x2(b.z, b.w);
-                if (p.out_mc != nullptr) multimem_st_bf16x8(p.out_mc + e, o);
-                else for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.out_ptrs[r] + e) = o;
+#pragma unroll
+                for (int u = 0; u < kUnroll; ++u) {
+                    const long long v = vb + u * stride;
+                    if (v < v1) {
+                        if (p.out_mc != nullptr) arc::broadcast8<true>(p.out_ptrs, p.out_mc, p.world, base + v * 8, o[u]);
+                        else arc::broadcast8<false>(p.out_ptrs, p.out_mc, p.world, base + v * 8, o[u]);
+                    }
+                }
             }
         }
         // every rank's broadcasts into this rank's output must have landed before the kernel ends
@@ -389,9 +352,9 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 __threadfence_system();
                 if (atomicAdd(p.counters + kMaxGroups, 1u) + 1u == gridDim.x)
                     for (int r = 0; r < p.world; ++r)
-                        st_release_sys_u32(p.flag_ptrs[r] + p.flag_offset_words + kMaxGroups * kMaxWorld + p.rank, p.epoch);
+                        arc::st_release_sys(p.flag_ptrs[r] + p.flag_offset_words + kMaxGroups * kMaxWorld + p.rank, p.epoch);
             }
-            if (rt < p.world) wait_flag_sys(my_flags + kMaxGroups * kMaxWorld + rt, p.epoch, p.status, 6);
+            if (rt < p.world) arc::wait_flag(my_flags + kMaxGroups * kMaxWorld + rt, p.epoch, p.status, 6);
         }
     }
 

@@ -17,7 +17,7 @@ Per rank and forward pass:
      all-reduce are ONE kernel (b200q_gemm_fp8_rowcol_allreduce) — finished row groups are summed
      in the NVSwitch (multimem.ld_reduce), rounded once to bf16 and broadcast (multimem.st) while
      later groups are still being multiplied.  ``comm="symm"``: the stand-alone NVSwitch kernel
-     (b200q_allreduce_f32_to_bf16) per token chunk on a side stream; ``comm="nccl"``:
+     (b200q_allreduce_to_bf16) per token chunk on a side stream; ``comm="nccl"``:
      torch.distributed.all_reduce + a cast.  All three keep fp32 accumulation and identical replicas.
 """
 from __future__ import annotations
@@ -51,7 +51,8 @@ class TensorParallelMLP:
 
     def __init__(self, w_gate, s_gate, w_up, s_up, w_down, s_down, rank: int = 0, world: int = 1,
                  group=None, device=None, max_tokens: int = 4096, chunks: int | None = None,
-                 presharded: bool = False, comm: str = "auto", ar_ctas: int = 32):
+                 presharded: bool = False, comm: str = "auto", ar_ctas: int = 64, partial_dtype=torch.bfloat16,
+                 use_multicast: bool = False):
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
         if presharded:      # the caller already holds only this rank's shard
@@ -75,6 +76,14 @@ class TensorParallelMLP:
         self.comm_stream = torch.cuda.Stream(device=dev) if world > 1 else None
         self.comm = "none"
         self.ar_ctas = ar_ctas
+        # Partial outputs travel as bf16 by default (half the NVLink bytes; the all-reduce then is
+        # "fp32 sum of the ranks' bf16 partials in rank order, one rounding"); torch.float32 keeps the
+        # reference's ncclFloat behaviour exactly.  Plain peer loads/stores by default: they are
+        # bit-reproducible and were faster than the in-switch reduction in measurements.
+        if partial_dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("partial_dtype must be torch.bfloat16 or torch.float32")
+        self.partial_dtype = partial_dtype
+        self.use_multicast = use_multicast
         self._epoch = 0
         if world > 1:
             self.comm = comm
@@ -89,9 +98,10 @@ class TensorParallelMLP:
             if self.comm == "fused":
                 self.chunks = 1
             if self.comm == "nccl":
-                self.partial = torch.empty((T, H), dtype=torch.float32, device=dev)
+                self.partial = torch.empty((T, H), dtype=self.partial_dtype, device=dev)
         self.kernel_launches_per_forward = 0
         self.top_kernel_events = None     # set to a list to collect (start, end) events of the gate/up kernel
+        self.stage_events = None          # set to a list to collect 5 events bracketing the 4 kernels of a stage
 
     def _init_symmetric(self, T, H):
         """Partial sums, output and barrier flags in symmetric memory (peer-mapped on every rank,
@@ -100,7 +110,7 @@ class TensorParallelMLP:
         import torch.distributed._symmetric_memory as symm
         group = self.group if self.group is not None else dist.group.WORLD
         dev = self.device
-        self.partial = symm.empty((T, H), dtype=torch.float32, device=dev)
+        self.partial = symm.empty((T, H), dtype=self.partial_dtype, device=dev)
         self.y_sym = symm.empty((T, H), dtype=torch.bfloat16, device=dev)
         self._fused_flag_offset = ops.lib().b200q_allreduce_signal_bytes()
         nflags = (self._fused_flag_offset + ops.lib().b200q_fused_allreduce_flag_bytes()) // 4
@@ -110,7 +120,7 @@ class TensorParallelMLP:
         self._hp = symm.rendezvous(self.partial, group)
         self._hy = symm.rendezvous(self.y_sym, group)
         self._hf = symm.rendezvous(self.flags, group)
-        self.multicast = bool(self._hp.multicast_ptr) and bool(self._hy.multicast_ptr)
+        self.multicast = self.use_multicast and bool(self._hp.multicast_ptr) and bool(self._hy.multicast_ptr)
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
 
@@ -120,10 +130,10 @@ class TensorParallelMLP:
         H = self.hidden
         mc_p = self._hp.multicast_ptr if self.multicast else None
         mc_y = self._hy.multicast_ptr if self.multicast else None
-        ops._raise(ops.lib().b200q_allreduce_f32_to_bf16(
+        ops._raise(ops.lib().b200q_allreduce_to_bf16(
             self._hp.buffer_ptrs_dev, self._hy.buffer_ptrs_dev, self._hf.buffer_ptrs_dev, mc_p, mc_y,
-            lo * H, (hi - lo) * H, self.rank, self.world, self._epoch, 0, self.ar_ctas,
-            torch.cuda.current_stream().cuda_stream), "b200q_allreduce_f32_to_bf16")
+            int(self.partial_dtype == torch.bfloat16), lo * H, (hi - lo) * H, self.rank, self.world, self._epoch, 0, self.ar_ctas,
+            torch.cuda.current_stream().cuda_stream), "b200q_allreduce_to_bf16")
 
     def _stage(self, x, y, lo, hi):
         """Steps 1-4 for tokens [lo, hi) on the current stream; returns the number of launches."""
@@ -131,7 +141,14 @@ class TensorParallelMLP:
         n = hi - lo
         H, Il = self.hidden, self.inter_local
         xq, sx, h, hq, shs = self.xq[lo:hi], self.sx[lo:hi], self.h[lo:hi], self.hq[lo:hi], self.shs[lo:hi]
+        marks = [] if self.stage_events is not None else None
+
+        def mark():
+            if marks is not None:
+                e = torch.cuda.Event(enable_timing=True); e.record(); marks.append(e)
+        mark()
         ops._raise(L.b200q_quant_rows_e4m3(x[lo:hi].data_ptr(), xq.data_ptr(), sx.data_ptr(), n, H, st), "quant x")
+        mark()
         ev = self.top_kernel_events
         if ev is not None:
             e0 = torch.cuda.Event(enable_timing=True); e0.record()
@@ -141,7 +158,9 @@ class TensorParallelMLP:
         if ev is not None:
             e1 = torch.cuda.Event(enable_timing=True); e1.record()
             ev.append((e0, e1))
+        mark()
         ops._raise(L.b200q_quant_rows_e4m3(h.data_ptr(), hq.data_ptr(), shs.data_ptr(), n, Il, st), "quant h")
+        mark()
         if self.world == 1:
             ops._raise(L.b200q_gemm_fp8_rowcol(hq.data_ptr(), self.wd.data_ptr(), y[lo:hi].data_ptr(), n, H, Il,
                                                shs.data_ptr(), self.sd.data_ptr(), 0, st), "down")
@@ -154,11 +173,15 @@ class TensorParallelMLP:
             ops._raise(L.b200q_gemm_fp8_rowcol_allreduce(
                 hq.data_ptr(), self.wd.data_ptr(), self.partial.data_ptr(), n, H, Il, shs.data_ptr(), self.sd.data_ptr(),
                 self._hp.buffer_ptrs_dev, self._hy.buffer_ptrs_dev, self._hf.buffer_ptrs_dev, mc_p, mc_y,
-                self._counters.data_ptr(), self._fused_flag_offset, self._epoch, self.rank, self.world, st),
+                int(self.partial_dtype == torch.bfloat16), self._counters.data_ptr(), self._fused_flag_offset, self._epoch, self.rank, self.world, st),
                 "down + all-reduce")
         else:
             ops._raise(L.b200q_gemm_fp8_rowcol(hq.data_ptr(), self.wd.data_ptr(), self.partial[lo:hi].data_ptr(),
-                                               n, H, Il, shs.data_ptr(), self.sd.data_ptr(), 1, st), "down")
+                                               n, H, Il, shs.data_ptr(), self.sd.data_ptr(),
+                                               int(self.partial_dtype == torch.float32), st), "down")
+        mark()
+        if marks is not None:
+            self.stage_events.append(marks)
         return 4
 
     def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
@@ -196,7 +219,7 @@ class TensorParallelMLP:
                             launches += 1
                         else:
                             dist.all_reduce(self.partial[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
-                            y[lo:hi].copy_(self.partial[lo:hi])     # fp32 -> bf16, round-to-nearest-even
+                            y[lo:hi].copy_(self.partial[lo:hi])     # (fp32 ->) bf16, round-to-nearest-even
                 main.wait_stream(self.comm_stream)
                 if self.comm == "symm" and out is not None:
                     out[:T].copy_(y)

@@ -93,7 +93,7 @@ int b200q_sp24_set_tile_n(int bn);
 int b200q_quant_rows_e4m3(const void* X, void* Q, float* S, int rows, int cols, void* stream);
 
 /* Sum all-reduce of the MLP's fp32 partial outputs over NVLink / NVSwitch, one call per rank, all
- * ranks at the same time: Y(bf16, on every rank) = sum_r P_r(fp32).  Replaces the in-place
+ * ranks at the same time: Y(bf16, on every rank) = sum_r P_r, P_r fp32 or (partial_is_bf16) bf16.  Replaces the in-place
  * ncclAllReduce(ncclFloat, ncclSum) of op/nccl/nccl_mlp_test.cu:181-195 with the same contract
  * (fp32 accumulation, bit-identical replicas).  The three pointer arguments are DEVICE arrays of
  * `world` pointers to every rank's partial buffer, output buffer and flag buffer (peer-mapped
@@ -101,26 +101,27 @@ int b200q_quant_rows_e4m3(const void* X, void* Q, float* S, int rows, int cols, 
  * zeroed once before the first call).  With multicast addresses of the partial and output buffers
  * the switch does the additions and the broadcast; pass NULL for both to use plain peer loads and
  * stores.  `epoch` must grow by one per call, identically on every rank; elems % (8 * world) == 0. */
-int b200q_allreduce_f32_to_bf16(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
-                                void* const* signal_ptrs_dev, const void* partial_multicast, void* out_multicast,
-                                long long elem_offset, long long elems, int rank, int world, unsigned int epoch,
-                                unsigned int signal_offset_bytes, int ctas, void* stream);
+int b200q_allreduce_to_bf16(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                            void* const* signal_ptrs_dev, const void* partial_multicast, void* out_multicast,
+                            int partial_is_bf16, long long elem_offset, long long elems, int rank, int world,
+                            unsigned int epoch, unsigned int signal_offset_bytes, int ctas, void* stream);
+int b200q_allreduce_set_unroll(int unroll);     /* tuning knob: independent reductions in flight per thread, 1..8 */
 size_t b200q_allreduce_signal_bytes(void);
 
 /* The MLP's row-parallel down projection with the all-reduce fused into the same kernel (one
  * kernel in place of GEMM -> ncclAllReduce, op/nccl/nccl_mlp_test.cu:170-195): every rank calls it
- * at the same time; the kernel writes fp32 partial tiles to `partial_local` (this rank's entry of
+ * at the same time; the kernel writes partial tiles (fp32, or bf16 with partial_is_bf16) to `partial_local` (this rank's entry of
  * partial_ptrs_dev), and while later row groups are still being multiplied its reducer warps sum
  * finished groups across ranks through NVSwitch and broadcast the bf16 result to every rank's
- * output.  Pointer-array, multicast, epoch and flag arguments as for b200q_allreduce_f32_to_bf16;
+ * output.  Pointer-array, multicast, epoch and flag arguments as for b200q_allreduce_to_bf16;
  * the flag buffer needs b200q_fused_allreduce_flag_bytes() bytes from flag_offset_bytes on (zeroed
  * once), `counters_local` is b200q_fused_allreduce_counter_bytes() of this rank's own memory. */
 int b200q_gemm_fp8_rowcol_allreduce(const void* A, const void* B, void* partial_local, int M, int N, int K,
                                     const float* row_scale, const float* col_scale,
                                     const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
                                     void* const* flag_ptrs_dev, const void* partial_multicast, void* out_multicast,
-                                    void* counters_local, unsigned int flag_offset_bytes, unsigned int epoch, int rank,
-                                    int world, void* stream);
+                                    int partial_is_bf16, void* counters_local, unsigned int flag_offset_bytes,
+                                    unsigned int epoch, int rank, int world, void* stream);
 size_t b200q_fused_allreduce_flag_bytes(void);
 size_t b200q_fused_allreduce_counter_bytes(void);
 

@@ -14,7 +14,7 @@ def _need_two():
         pytest.skip("needs 2 GPUs")
 
 
-def _worker(rank, world, port, mode, out_dir):
+def _worker(rank, world, port, mode, pdt, out_dir):
     import torch.distributed as dist
     import cudaop_b200 as ops
     from cudaop_b200.mlp import TensorParallelMLP
@@ -26,9 +26,9 @@ def _worker(rank, world, port, mode, out_dir):
     case = oracle.make_mlp_case(T, H, I, seed=31)
     ts = [torch.from_numpy(np.ascontiguousarray(t)) for t in case[1:]]
     comm = {"multicast": "symm", "p2p": "symm", "nccl": "nccl", "fused": "fused", "fused_p2p": "fused"}[mode]
-    mlp = TensorParallelMLP(*ts, rank=rank, world=world, max_tokens=T, chunks=2, comm=comm)
-    if mode in ("p2p", "fused_p2p"):
-        mlp.multicast = False
+    pdtype = torch.bfloat16 if pdt == "bf16" else torch.float32
+    mlp = TensorParallelMLP(*ts, rank=rank, world=world, max_tokens=T, chunks=2, comm=comm, partial_dtype=pdtype,
+                            use_multicast=mode in ("multicast", "fused"))
     x = torch.from_numpy(case[0].view(np.int16)).cuda().view(torch.bfloat16)
     y = mlp(x).clone()
     y2 = mlp(x).clone()                       # a second pass reuses buffers and flags
@@ -41,25 +41,30 @@ def _worker(rank, world, port, mode, out_dir):
     else:
         parts = [torch.empty_like(mlp.partial) for _ in range(world)]
         dist.all_gather(parts, mlp.partial.contiguous())
-        want = sum(p for p in parts).to(torch.bfloat16)
+        acc = torch.zeros_like(parts[0], dtype=torch.float32)
+        for p in parts:                                # fp32 sum in rank order, one rounding
+            acc += p.float()
+        want = acc.to(torch.bfloat16)
     torch.save({"y": y.cpu(), "want": want.cpu(), "comm": mlp.comm, "mc": getattr(mlp, "multicast", None)},
-               os.path.join(out_dir, f"{mode}_r{rank}.pt"))
+               os.path.join(out_dir, f"{mode}_{pdt}_r{rank}.pt"))
     dist.barrier(); dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("pdt", ["bf16", "fp32"])
 @pytest.mark.parametrize("mode", ["fused", "fused_p2p", "multicast", "p2p", "nccl"])
-def test_two_rank_mlp_allreduce(mode, tmp_path):
+def test_two_rank_mlp_allreduce(mode, pdt, tmp_path):
     _need_two()
     import torch.multiprocessing as mp
-    port = 29600 + (os.getpid() % 1000) + {"multicast": 0, "p2p": 1, "nccl": 2, "fused": 3, "fused_p2p": 4}[mode]
-    mp.spawn(_worker, args=(2, port, mode, str(tmp_path)), nprocs=2, join=True)
-    r0 = torch.load(tmp_path / f"{mode}_r0.pt"); r1 = torch.load(tmp_path / f"{mode}_r1.pt")
+    port = 29600 + (os.getpid() % 1000) + {"multicast": 0, "p2p": 1, "nccl": 2, "fused": 3, "fused_p2p": 4}[mode] + (5 if pdt == "fp32" else 0)
+    mp.spawn(_worker, args=(2, port, mode, pdt, str(tmp_path)), nprocs=2, join=True)
+    r0 = torch.load(tmp_path / f"{mode}_{pdt}_r0.pt"); r1 = torch.load(tmp_path / f"{mode}_{pdt}_r1.pt")
     print(mode, "comm:", r0["comm"], "multicast:", r0["mc"])
     assert torch.equal(r0["y"], r1["y"])                # replicas bit-identical (nccl_mlp_test.cu:646-664)
-    if mode == "nccl":
+    if mode in ("nccl", "p2p", "fused_p2p"):
+        # plain peer loads: fp32 sum in rank order, one rounding -- bit for bit
         assert torch.equal(r0["y"], r0["want"])
     else:
         # one rounding of the fp32 sum; the switch may add in a different order than rank order
         d = (r0["y"].float() - r0["want"].float()).abs().max().item()
         assert d <= 2.0 ** -7 * r0["want"].float().abs().max().item()
-        assert (r0["y"] == r0["want"]).float().mean().item() > 0.99
+        assert (r0["y"] == r0["want"]).float().mean().item() > (0.99 if pdt == "fp32" else 0.7)
