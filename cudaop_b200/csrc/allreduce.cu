@@ -82,17 +82,15 @@ allreduce_to_bf16_kernel(const Params p)
     const long long stride = static_cast<long long>(gridDim.x) * kThreads;
     for (long long vb = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; vb < vecs; vb += stride * UNROLL) {
         uint4 o[UNROLL];
+        long long e[UNROLL];
+        bool valid[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) { valid[u] = vb + u * stride < vecs; e[u] = base + (vb + u * stride) * 8; }
+        arc::reduce8xU<MC, PartialBf16, UNROLL>(reinterpret_cast<const void* const*>(p.partial_ptrs), p.partial_mc, p.world,
+                                                e, valid, o);
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u)
-            if (vb + u * stride < vecs)
-                o[u] = arc::reduce8<MC, PartialBf16>(reinterpret_cast<const void* const*>(p.partial_ptrs), p.partial_mc, p.world,
-                                                     base + (vb + u * stride) * 8);
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
-            if (vb + u * stride < vecs) {
-                const long long e = base + (vb + u * stride) * 8;
-                arc::broadcast8<MC>(p.out_ptrs, p.out_mc, p.world, e, o[u]);
-            }
+            if (valid[u]) arc::broadcast8<MC>(p.out_ptrs, p.out_mc, p.world, e[u], o[u]);
     }
     rank_barrier(p, 1, dummy);
 }

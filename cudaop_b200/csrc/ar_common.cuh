@@ -92,6 +92,61 @@ __device__ __forceinline__ uint4 reduce8(const void* const* partial_ptrs, const 
     return make_uint4(pack_bf16x2(a.x, a.y), pack_bf16x2(a.z, a.w), pack_bf16x2(b.x, b.y), pack_bf16x2(b.z, b.w));
 }
 
+// The same sum for U independent groups of eight values at once (elements e[0..U)).  All loads of
+// one rank are issued before any addition, so U (x2 for fp32) 16-byte requests per rank are in
+// flight per thread: throughput over NVLink comes from the number of outstanding loads.
+template <bool MC, bool PartialBf16, int U>
+__device__ __forceinline__ void reduce8xU(const void* const* partial_ptrs, const void* partial_mc, int world,
+                                          const long long (&e)[U], const bool (&valid)[U], uint4 (&out)[U])
+{
+    if (MC) {
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (valid[u]) out[u] = reduce8<true, PartialBf16>(partial_ptrs, partial_mc, world, e[u]);
+        return;
+    }
+    float acc[U][8];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[u][i] = 0.0f;
+    for (int r = 0; r < world; ++r) {                  // fixed rank order
+        if (PartialBf16) {
+            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(partial_ptrs[r]);
+            uint4 x[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u)
+                x[u] = valid[u] ? __ldcg(reinterpret_cast<const uint4*>(src + e[u])) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const uint32_t w[4] = {x[u].x, x[u].y, x[u].z, x[u].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    acc[u][2 * i] += __uint_as_float(w[i] << 16);
+                    acc[u][2 * i + 1] += __uint_as_float(w[i] & 0xFFFF0000u);
+                }
+            }
+        } else {
+            const float* src = static_cast<const float*>(partial_ptrs[r]);
+            float4 x[U], y[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                x[u] = valid[u] ? __ldcg(reinterpret_cast<const float4*>(src + e[u])) : make_float4(0, 0, 0, 0);
+                y[u] = valid[u] ? __ldcg(reinterpret_cast<const float4*>(src + e[u]) + 1) : make_float4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                acc[u][0] += x[u].x; acc[u][1] += x[u].y; acc[u][2] += x[u].z; acc[u][3] += x[u].w;
+                acc[u][4] += y[u].x; acc[u][5] += y[u].y; acc[u][6] += y[u].z; acc[u][7] += y[u].w;
+            }
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+        out[u] = make_uint4(pack_bf16x2(acc[u][0], acc[u][1]), pack_bf16x2(acc[u][2], acc[u][3]),
+                            pack_bf16x2(acc[u][4], acc[u][5]), pack_bf16x2(acc[u][6], acc[u][7]));
+}
+
 template <bool MC>
 __device__ __forceinline__ void broadcast8(__nv_bfloat16* const* out_ptrs, __nv_bfloat16* out_mc, int world, long long e, uint4 o)
 {

@@ -326,23 +326,19 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (long long vb = v0 + blockIdx.x * static_cast<long long>(kReducerThreads) + rt; vb < v1;
                  vb += stride * kUnroll) {
                 uint4 o[kUnroll];
+                long long e[kUnroll];
+                bool valid[kUnroll];
                 constexpr bool kBf = sizeof(OutT) == 2;          // partial tiles are stored as OutT
 #pragma unroll
-                for (int u = 0; u < kUnroll; ++u) {
-                    const long long v = vb + u * stride;
-                    if (v < v1) {
-                        if (p.partial_mc != nullptr) o[u] = arc::reduce8<true, kBf>(p.partial_ptrs, p.partial_mc, p.world, base + v * 8);
-                        else o[u] = arc::reduce8<false, kBf>(p.partial_ptrs, p.partial_mc, p.world, base + v * 8);
-                    }
-                }
+                for (int u = 0; u < kUnroll; ++u) { valid[u] = vb + u * stride < v1; e[u] = base + (vb + u * stride) * 8; }
+                if (p.partial_mc != nullptr) arc::reduce8xU<true, kBf, kUnroll>(p.partial_ptrs, p.partial_mc, p.world, e, valid, o);
+                else arc::reduce8xU<false, kBf, kUnroll>(p.partial_ptrs, p.partial_mc, p.world, e, valid, o);
 #pragma unroll
-                for (int u = 0; u < kUnroll; ++u) {
-                    const long long v = vb + u * stride;
-                    if (v < v1) {
-                        if (p.out_mc != nullptr) arc::broadcast8<true>(p.out_ptrs, p.out_mc, p.world, base + v * 8, o[u]);
-                        else arc::broadcast8<false>(p.out_ptrs, p.out_mc, p.world, base + v * 8, o[u]);
+                for (int u = 0; u < kUnroll; ++u)
+                    if (valid[u]) {
+                        if (p.out_mc != nullptr) arc::broadcast8<true>(p.out_ptrs, p.out_mc, p.world, e[u], o[u]);
+                        else arc::broadcast8<false>(p.out_ptrs, p.out_mc, p.world, e[u], o[u]);
                     }
-                }
             }
         }
         // every rank's broadcasts into this rank's output must have landed before the kernel ends
