@@ -289,14 +289,18 @@ def run_ours(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, finish=None):
         for _ in range(warmup):
             fn()
+        if finish:
+            finish()
         sync_all()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             fn()
+        if finish:
+            finish()            # the timed stream waits for every side-stream all-reduce of the K steps
         e1.record()
         sync_all()
         ms = e0.elapsed_time(e1)
@@ -311,7 +315,7 @@ def run_ours(args):
         sampler.start()
     # ---- device-resident steps (the headline `value`) with events around the top kernel
     mlp.top_kernel_events = []
-    ms_step = timed(lambda: mlp.forward(x), args.steps, args.warmup)
+    ms_step = timed(lambda: mlp.forward(x), args.steps, args.warmup, finish=mlp.wait)
     evs = mlp.top_kernel_events; mlp.top_kernel_events = None
     torch.cuda.synchronize()
     top_ms = [a.elapsed_time(b) for a, b in evs[-args.steps * max(1, mlp.chunks if world > 1 else 1):]]
@@ -324,11 +328,31 @@ def run_ours(args):
     names = ("quant_x", "gate_up_swiglu", "quant_h", "down_allreduce" if world > 1 else "down")
     kernels_ms = {n: min(m[i].elapsed_time(m[i + 1]) for m in mlp.stage_events) for i, n in enumerate(names)}
     mlp.stage_events = None
-    # ---- end to end: pinned host input -> device, forward, result back to pinned host memory
+    # ---- latency of ONE forward with nothing else in flight (N > 1: the fused GEMM + all-reduce kernel)
+    if world > 1:
+        lat = TensorParallelMLP(mlp.wg, mlp.sg, mlp.wu, mlp.su, mlp.wd, mlp.sd, rank=rank, world=world, device=dev,
+                                max_tokens=TOKENS, presharded=True, comm="fused", use_multicast=args.multicast,
+                                partial_dtype=mlp.partial_dtype)
+        ms_latency = timed(lambda: lat.forward(x), args.steps, args.warmup)
+    else:
+        ms_latency = ms_step
+    # ---- end to end: every step takes its input from pinned host memory and leaves its result there.
+    # With R ranks each rank moves 1/R of X over its own PCIe link and the ranks all-gather X over NVLink;
+    # each rank writes back 1/R of the (replicated) result.
+    rows = TOKENS // world
+    lo, hi = rank * rows, (rank + 1) * rows
     def e2e_step():
-        x.copy_(x_host, non_blocking=True)
-        y_host.copy_(mlp.forward(x), non_blocking=True)
-    ms_e2e = timed(e2e_step, args.steps, args.warmup)
+        if world == 1:
+            x.copy_(x_host, non_blocking=True)
+            y_host.copy_(mlp.forward(x), non_blocking=True)
+            return
+        x[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+        dist.all_gather_into_tensor(x, x[lo:hi].clone())
+        yy = mlp.forward(x)
+        side = mlp.comm_stream if mlp.comm == "pipelined" else torch.cuda.current_stream()
+        with torch.cuda.stream(side):                 # ordered after this step's all-reduce
+            y_host[lo:hi].copy_(yy[lo:hi], non_blocking=True)
+    ms_e2e = timed(e2e_step, args.steps, args.warmup, finish=mlp.wait)
     clocks = sampler.stop() if sampler else None
     assert ops.status() == 0, "a kernel gave up on a bounded wait"
 
@@ -352,7 +376,13 @@ def run_ours(args):
         "tflops": MLP_FLOPS / (ms_step * 1e-3) / 1e12,
         "clocks": clocks,
         "e2e": {"value": TOKENS / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": TOKENS * HIDDEN * 2, "d2h_bytes_per_step": TOKENS * HIDDEN * 2},
+                "h2d_bytes_per_step": TOKENS * HIDDEN * 2, "d2h_bytes_per_step": TOKENS * HIDDEN * 2,
+                "note": "whole-job bytes; with R ranks each rank copies 1/R of X in and 1/R of Y out over its own "
+                        "PCIe link, X is all-gathered over NVLink"},
+        "latency_ms_per_forward": ms_latency,
+        "overlap": ("steps are independent batches: the all-reduce of step i runs on a side stream under the GEMMs "
+                    "of step i+1 (double-buffered); latency_ms_per_forward is one forward alone with the all-reduce "
+                    "fused into the down-projection kernel") if world > 1 and mlp.comm == "pipelined" else "none",
         "gpu_launches": launches, "kernels_ms": kernels_ms,
         "roofline": {"bound": "tensor", "kernel": "gemm_fp8_kernel<SwiGLU> (gate/up projection)",
                      "achieved": top_tf, "peak": peak, "unit": "TFLOP/s", "frac": top_tf / peak,
@@ -388,7 +418,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chunks", type=int, default=4, help="token chunks for all-reduce overlap (N > 1)")
-    ap.add_argument("--comm", default="auto", choices=["auto", "fused", "symm", "nccl"],
+    ap.add_argument("--comm", default="pipelined", choices=["auto", "pipelined", "fused", "symm", "nccl"],
                     help="all-reduce: the library's NVSwitch kernel over symmetric memory, or NCCL")
     ap.add_argument("--ar-ctas", type=int, default=64)
     ap.add_argument("--partial", default="bf16", choices=["bf16", "fp32"], help="dtype of the partial outputs that cross NVLink")

@@ -19,6 +19,10 @@ Per rank and forward pass:
      later groups are still being multiplied.  ``comm="symm"``: the stand-alone NVSwitch kernel
      (b200q_allreduce_to_bf16) per token chunk on a side stream; ``comm="nccl"``:
      torch.distributed.all_reduce + a cast.  All three keep fp32 accumulation and identical replicas.
+     ``comm="pipelined"``: as "symm" with one chunk, but forward() does not wait for the all-reduce:
+     it runs on the side stream under the NEXT forward's GEMMs (independent batches), partials and
+     outputs double-buffered; the caller orders its use of Y after ``output_ready`` (an event) or
+     calls ``wait()``.  Throughput mode for a stream of batches; "fused" is the latency mode.
 """
 from __future__ import annotations
 
@@ -87,16 +91,20 @@ class TensorParallelMLP:
         self._epoch = 0
         if world > 1:
             self.comm = comm
-            if comm in ("auto", "fused", "symm"):
+            if comm in ("auto", "fused", "symm", "pipelined"):
                 try:
+                    self._nbuf = 2 if comm == "pipelined" else 1
                     self._init_symmetric(T, H)
-                    self.comm = "symm" if comm == "symm" else "fused"
+                    self.comm = comm if comm in ("symm", "pipelined") else "fused"
                 except Exception:
                     if comm != "auto":
                         raise
                     self.comm = "nccl"
-            if self.comm == "fused":
+            if self.comm in ("fused", "pipelined"):
                 self.chunks = 1
+            self._buf = 0
+            self._ar_done = [None, None]
+            self.output_ready = None
             if self.comm == "nccl":
                 self.partial = torch.empty((T, H), dtype=self.partial_dtype, device=dev)
         self.kernel_launches_per_forward = 0
@@ -110,24 +118,29 @@ class TensorParallelMLP:
         import torch.distributed._symmetric_memory as symm
         group = self.group if self.group is not None else dist.group.WORLD
         dev = self.device
-        self.partial = symm.empty((T, H), dtype=self.partial_dtype, device=dev)
-        self.y_sym = symm.empty((T, H), dtype=torch.bfloat16, device=dev)
+        nb = getattr(self, "_nbuf", 1)
+        self._partial_all = symm.empty((nb, T, H), dtype=self.partial_dtype, device=dev)
+        self._y_all = symm.empty((nb, T, H), dtype=torch.bfloat16, device=dev)
+        self.partial = self._partial_all[0]
+        self.y_sym = self._y_all[0]
         self._fused_flag_offset = ops.lib().b200q_allreduce_signal_bytes()
         nflags = (self._fused_flag_offset + ops.lib().b200q_fused_allreduce_flag_bytes()) // 4
         self._counters = torch.zeros((ops.lib().b200q_fused_allreduce_counter_bytes() // 4,), dtype=torch.int32, device=dev)
         self.flags = symm.empty((nflags,), dtype=torch.int32, device=dev)
         self.flags.zero_()
-        self._hp = symm.rendezvous(self.partial, group)
-        self._hy = symm.rendezvous(self.y_sym, group)
+        self._hp = symm.rendezvous(self._partial_all, group)
+        self._hy = symm.rendezvous(self._y_all, group)
         self._hf = symm.rendezvous(self.flags, group)
         self.multicast = self.use_multicast and bool(self._hp.multicast_ptr) and bool(self._hy.multicast_ptr)
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
 
-    def _allreduce_chunk(self, lo, hi):
-        """Launches the all-reduce kernel for tokens [lo, hi) on the current stream."""
+    def _allreduce_chunk(self, lo, hi, buf: int = 0):
+        """Launches the all-reduce kernel for tokens [lo, hi) of buffer `buf` on the current stream."""
         self._epoch += 1
         H = self.hidden
+        lo += buf * self.max_tokens
+        hi += buf * self.max_tokens
         mc_p = self._hp.multicast_ptr if self.multicast else None
         mc_y = self._hy.multicast_ptr if self.multicast else None
         ops._raise(ops.lib().b200q_allreduce_to_bf16(
@@ -189,6 +202,8 @@ class TensorParallelMLP:
         T, H = x.shape
         if H != self.hidden or T > self.max_tokens:
             raise ValueError(f"x must be [<= {self.max_tokens}, {self.hidden}]")
+        if self.comm == "pipelined":
+            return self._forward_pipelined(x, T)
         if self.comm in ("symm", "fused"):
             y = self.y_sym[:T]
         else:
@@ -226,5 +241,31 @@ class TensorParallelMLP:
                     y = out
         self.kernel_launches_per_forward = launches
         return y
+
+    def _forward_pipelined(self, x, T):
+        """GEMMs on the current stream, all-reduce on the side stream; returns this step's output
+        buffer, which is complete once ``self.output_ready`` has fired."""
+        b = self._buf
+        self._buf ^= 1
+        main = torch.cuda.current_stream()
+        with torch.cuda.device(self.device):
+            if self._ar_done[b] is not None:            # the all-reduce that last read partial[b] / wrote y[b]
+                main.wait_event(self._ar_done[b])
+            self.partial = self._partial_all[b]
+            launches = self._stage(x, None, 0, T)
+            done = torch.cuda.Event(); done.record(main)
+            with torch.cuda.stream(self.comm_stream):
+                self.comm_stream.wait_event(done)
+                self._allreduce_chunk(0, T, buf=b)
+                ev = torch.cuda.Event(); ev.record(self.comm_stream)
+            self._ar_done[b] = ev
+            self.output_ready = ev
+        self.kernel_launches_per_forward = launches + 1
+        return self._y_all[b][:T]
+
+    def wait(self):
+        """Makes the current stream wait for every all-reduce issued so far."""
+        if self.comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
 
     __call__ = forward

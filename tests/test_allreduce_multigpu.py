@@ -25,13 +25,16 @@ def _worker(rank, world, port, mode, pdt, out_dir):
     T, H, I = 1200, 512, 1024           # 10 tile rows: three row groups in the fused kernel, ragged last
     case = oracle.make_mlp_case(T, H, I, seed=31)
     ts = [torch.from_numpy(np.ascontiguousarray(t)) for t in case[1:]]
-    comm = {"multicast": "symm", "p2p": "symm", "nccl": "nccl", "fused": "fused", "fused_p2p": "fused"}[mode]
+    comm = {"multicast": "symm", "p2p": "symm", "nccl": "nccl", "fused": "fused", "fused_p2p": "fused",
+            "pipelined": "pipelined"}[mode]
     pdtype = torch.bfloat16 if pdt == "bf16" else torch.float32
     mlp = TensorParallelMLP(*ts, rank=rank, world=world, max_tokens=T, chunks=2, comm=comm, partial_dtype=pdtype,
                             use_multicast=mode in ("multicast", "fused"))
     x = torch.from_numpy(case[0].view(np.int16)).cuda().view(torch.bfloat16)
-    y = mlp(x).clone()
-    y2 = mlp(x).clone()                       # a second pass reuses buffers and flags
+    y = mlp(x); mlp.wait(); y = y.clone()
+    y2 = mlp(x); mlp.wait(); y2 = y2.clone()   # a second pass reuses (or alternates) buffers and flags
+    y3 = mlp(x); mlp.wait()
+    assert torch.equal(y3, y)
     torch.cuda.synchronize()
     assert ops.status() == 0
     assert torch.equal(y, y2)
@@ -51,16 +54,16 @@ def _worker(rank, world, port, mode, pdt, out_dir):
 
 
 @pytest.mark.parametrize("pdt", ["bf16", "fp32"])
-@pytest.mark.parametrize("mode", ["fused", "fused_p2p", "multicast", "p2p", "nccl"])
+@pytest.mark.parametrize("mode", ["pipelined", "fused", "fused_p2p", "multicast", "p2p", "nccl"])
 def test_two_rank_mlp_allreduce(mode, pdt, tmp_path):
     _need_two()
     import torch.multiprocessing as mp
-    port = 29600 + (os.getpid() % 1000) + {"multicast": 0, "p2p": 1, "nccl": 2, "fused": 3, "fused_p2p": 4}[mode] + (5 if pdt == "fp32" else 0)
+    port = 29600 + (os.getpid() % 1000) + {"multicast": 0, "p2p": 1, "nccl": 2, "fused": 3, "fused_p2p": 4, "pipelined": 10}[mode] + (5 if pdt == "fp32" else 0)
     mp.spawn(_worker, args=(2, port, mode, pdt, str(tmp_path)), nprocs=2, join=True)
     r0 = torch.load(tmp_path / f"{mode}_{pdt}_r0.pt"); r1 = torch.load(tmp_path / f"{mode}_{pdt}_r1.pt")
     print(mode, "comm:", r0["comm"], "multicast:", r0["mc"])
     assert torch.equal(r0["y"], r1["y"])                # replicas bit-identical (nccl_mlp_test.cu:646-664)
-    if mode in ("nccl", "p2p", "fused_p2p"):
+    if mode in ("nccl", "p2p", "fused_p2p", "pipelined"):
         # plain peer loads: fp32 sum in rank order, one rounding -- bit for bit
         assert torch.equal(r0["y"], r0["want"])
     else:
