@@ -24,7 +24,7 @@ namespace ar {
 
 constexpr int kThreads = 512;
 constexpr int kMaxWorld = arc::kMaxWorld;
-constexpr int kMaxCtas = 128;
+constexpr int kMaxCtas = 256;
 
 struct Params {
     const float* const* partial_ptrs;     // device array [world]: every rank's partial buffer
@@ -73,6 +73,7 @@ template <bool MC, bool PartialBf16, int UNROLL>
 __global__ void __launch_bounds__(kThreads)
 allreduce_to_bf16_kernel(const Params p)
 {
+    const int kThreads = blockDim.x;          // 128..512: small blocks on every SM disturb a co-running GEMM evenly
     bool dummy = true;
     if (!rank_barrier(p, 0, dummy)) return;
 
@@ -96,6 +97,7 @@ allreduce_to_bf16_kernel(const Params p)
 }
 
 int g_unroll = 4;
+int g_threads = 512;
 
 }  // namespace ar
 }  // namespace b200q
@@ -130,7 +132,7 @@ int b200q_allreduce_to_bf16(const void* const* partial_ptrs_dev, void* const* ou
     if (p.status == nullptr) return cudaErrorInvalidDevice;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool mc = partial_multicast != nullptr;
-#define B200Q_AR(MC_, BF_, U_) ar::allreduce_to_bf16_kernel<MC_, BF_, U_><<<ctas, ar::kThreads, 0, s>>>(p)
+#define B200Q_AR(MC_, BF_, U_) ar::allreduce_to_bf16_kernel<MC_, BF_, U_><<<ctas, ar::g_threads, 0, s>>>(p)
 #define B200Q_AR_U(MC_, BF_) do { if (ar::g_unroll >= 8) B200Q_AR(MC_, BF_, 8); else if (ar::g_unroll >= 4) B200Q_AR(MC_, BF_, 4); else if (ar::g_unroll >= 2) B200Q_AR(MC_, BF_, 2); else B200Q_AR(MC_, BF_, 1); } while (0)
     if (partial_is_bf16) { if (mc) B200Q_AR_U(true, true); else B200Q_AR_U(false, true); }
     else { if (mc) B200Q_AR_U(true, false); else B200Q_AR_U(false, false); }
@@ -143,6 +145,13 @@ int b200q_allreduce_set_unroll(int unroll)
 {
     if (unroll < 1 || unroll > 8) return cudaErrorInvalidValue;
     b200q::ar::g_unroll = unroll;
+    return 0;
+}
+
+int b200q_allreduce_set_threads(int threads)
+{
+    if (threads != 128 && threads != 256 && threads != 512) return cudaErrorInvalidValue;
+    b200q::ar::g_threads = threads;
     return 0;
 }
 

@@ -8,6 +8,7 @@ namespace fp8 {
 namespace {
 
 int g_force_bn = 0;      // 0 = choose per problem; 224 or 256 = forced (b200q_fp8_set_tile_n)
+int g_reducer_stride = 1;
 
 template <int EPI, typename OutT, int BN, bool AR>
 cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2, const Params& p,
@@ -103,6 +104,7 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
         p.out_mc = static_cast<__nv_bfloat16*>(ar->out_mc);
         p.counters = static_cast<uint32_t*>(ar->counters);
         p.flag_offset_words = ar->flag_offset_bytes / 4; p.epoch = ar->epoch; p.rank = ar->rank; p.world = ar->world;
+        p.reducer_stride = g_reducer_stride;
         cudaError_t e = cudaMemsetAsync(p.counters, 0, (kMaxGroups + 1) * sizeof(uint32_t), stream);
         if (e != cudaSuccess) return e;
     }
@@ -176,6 +178,13 @@ size_t b200q_fused_allreduce_flag_bytes(void)
 size_t b200q_fused_allreduce_counter_bytes(void)
 {
     return static_cast<size_t>(b200q::fp8::kMaxGroups + 1) * sizeof(uint32_t);
+}
+
+int b200q_fp8_set_reducer_stride(int stride)
+{
+    if (stride < 1 || stride > 16) return cudaErrorInvalidValue;
+    b200q::fp8::g_reducer_stride = stride;
+    return 0;
 }
 
 int b200q_fp8_set_tile_n(int bn)

@@ -78,6 +78,7 @@ struct Params {
     uint32_t flag_offset_words;
     uint32_t epoch;
     int rank, world;
+    int reducer_stride;                  // only CTAs with blockIdx % reducer_stride == 0 reduce (1 = all)
 };
 
 template <typename OutT> struct OutPack;
@@ -321,9 +322,12 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const long long base = row0 * p.N;
             // kUnroll independent 32-byte reductions in flight per thread: the round trip through the
             // switch is microseconds, so throughput comes from the number of loads outstanding
-            constexpr int kUnroll = 4;
-            const long long stride = static_cast<long long>(gridDim.x) * kReducerThreads;
-            for (long long vb = v0 + blockIdx.x * static_cast<long long>(kReducerThreads) + rt; vb < v1;
+            constexpr int kUnroll = 8;
+            const int rstride = p.reducer_stride;
+            const long long nred = (gridDim.x + rstride - 1) / rstride;       // CTAs that take part
+            const long long stride = nred * kReducerThreads;
+            if (blockIdx.x % rstride != 0) continue;
+            for (long long vb = v0 + (blockIdx.x / rstride) * static_cast<long long>(kReducerThreads) + rt; vb < v1;
                  vb += stride * kUnroll) {
                 uint4 o[kUnroll];
                 long long e[kUnroll];

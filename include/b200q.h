@@ -84,6 +84,7 @@ int b200q_gemm_sp24_fp8(const void* Acomp, const void* Ameta, const void* B, voi
 
 /* Tuning knobs (process-wide): width of the B tile, 128 / 192 / 256 columns. */
 int b200q_fp8_set_tile_n(int bn);      /* 0 = chosen per problem (default), 224 or 256 */
+int b200q_fp8_set_reducer_stride(int stride);   /* fused all-reduce: every stride-th CTA reduces, 1..16 */
 int b200q_nvfp4_set_tile_n(int bn);
 int b200q_sp24_set_tile_n(int bn);
 
@@ -106,6 +107,7 @@ int b200q_allreduce_to_bf16(const void* const* partial_ptrs_dev, void* const* ou
                             int partial_is_bf16, long long elem_offset, long long elems, int rank, int world,
                             unsigned int epoch, unsigned int signal_offset_bytes, int ctas, void* stream);
 int b200q_allreduce_set_unroll(int unroll);     /* tuning knob: independent reductions in flight per thread, 1..8 */
+int b200q_allreduce_set_threads(int threads);   /* tuning knob: threads per CTA of the all-reduce kernel, 128/256/512 */
 size_t b200q_allreduce_signal_bytes(void);
 
 /* The MLP's row-parallel down projection with the all-reduce fused into the same kernel (one
