@@ -1,4 +1,5 @@
-// INT4 weight-only GEMM for decode shapes (M <= 16 per pass):
+// INT4 weight-only GEMM for decode shapes on warp-level mma.sync (kept as the alternative
+// implementation behind b200q_w4a16_set_impl(0); the default is the tcgen05 kernel in gemm_w4a16_tc.cu):
 //   Y[M,N] (bf16) = X[M,K] (bf16) * dequant(Wq)[N,K]^T,  w[n,k] = q[n,k] * S[n, k/128]
 // Wq packs two signed 4-bit weights per byte along K, low nibble = lower K index
 // (op/test/arch_primitives/ptx_mma_integer.cu:93-108); S is fp16, one scale per 128 K, no zero point.
@@ -157,8 +158,8 @@ w4a16_kernel(const __nv_bfloat16* __restrict__ X, const uint8_t* __restrict__ Wq
 }  // namespace w4a16
 }  // namespace b200q
 
-extern "C" int b200q_gemm_w4a16(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group,
-                                void* stream)
+extern "C" int b200q_gemm_w4a16_warp_mma(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K,
+                                         int group, void* stream)
 {
     using namespace b200q;
     if (X == nullptr || Wq == nullptr || S == nullptr || Y == nullptr) return cudaErrorInvalidValue;

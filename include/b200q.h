@@ -86,6 +86,8 @@ int b200q_gemm_sp24_fp8(const void* Acomp, const void* Ameta, const void* B, voi
 int b200q_fp8_set_tile_n(int bn);      /* 0 = chosen per problem (default), 224 or 256 */
 int b200q_fp8_set_reducer_stride(int stride);   /* fused all-reduce: every stride-th CTA reduces, 1..16 */
 int b200q_nvfp4_set_tile_n(int bn);
+int b200q_w4a16_set_impl(int impl);     /* 0 = warp-MMA kernel (default, measured faster), 1 = tcgen05 kernel */
+int b200q_w4a16_set_pdl(int on);        /* programmatic dependent launch of the tcgen05 W4A16 kernel (default off) */
 int b200q_sp24_set_tile_n(int bn);
 
 /* Activation quantiser: X[rows,cols] bf16 -> Q[rows,cols] E4M3 and S[rows] fp32,

@@ -9,6 +9,15 @@ from tests.util import CORES, assert_bar, bf16_to_f32, dev
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[1, 0], ids=["tcgen05", "warp_mma"], autouse=True)
+def impl(request):
+    """Both implementations behind b200q_gemm_w4a16: the tcgen05 kernel (default) and the warp-MMA one."""
+    import cudaop_b200 as ops
+    ops.lib().b200q_w4a16_set_impl(request.param)
+    yield request.param
+    ops.lib().b200q_w4a16_set_impl(0)
+
+
 def _w4_ref(xb, wq, s, group=128):
     return oracle.gemm_f32(oracle.decode_bf16(xb), oracle.dequant_w4(wq, s, group), threads=CORES)
 
