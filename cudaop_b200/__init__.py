@@ -28,6 +28,7 @@ _VP, _I, _F = C.c_void_p, C.c_int, C.c_float
 _SIZE_T_FUNCS = {
     "b200q_gemm_nvfp4_workspace_bytes": [C.c_int, C.c_int, C.c_int],
     "b200q_nvfp4_sf_bytes": [C.c_int, C.c_int],
+    "b200q_gemm_nvfp4_static_max_bytes": [],
     "b200q_allreduce_signal_bytes": [],
     "b200q_fused_allreduce_flag_bytes": [],
     "b200q_fused_allreduce_counter_bytes": [],
@@ -38,6 +39,7 @@ _SIGNATURES = {
     "b200q_gemm_fp8_swiglu": [_VP, _VP, _VP, _VP, _I, _I, _I, _VP, _VP, _VP, _VP],
     "b200q_gemm_w4a16": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP],
     "b200q_gemm_nvfp4": [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP, _VP],
+    "b200q_gemm_nvfp4_static": [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
     "b200q_gemm_nvfp4_blocked": [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
     "b200q_nvfp4_swizzle_sf": [_VP, _VP, _I, _I, _VP],
     "b200q_nvfp4_set_tile_n": [_I],

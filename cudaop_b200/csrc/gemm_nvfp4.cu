@@ -19,6 +19,9 @@
 #include "ptx.cuh"
 #include "../../include/b200q.h"
 
+#include <cstdio>
+#include <mutex>
+
 namespace b200q {
 namespace nvfp4 {
 
@@ -359,6 +362,85 @@ int b200q_gemm_nvfp4(const void* Aq, const void* SFA, const void* Bq, const void
     e = b200q_nvfp4_swizzle_sf(SFB, wb, N, K, stream);
     if (e != 0) return e;
     return b200q_gemm_nvfp4_blocked(Aq, wa, Bq, wb, C, M, N, K, global_a, global_b, stream);
+}
+
+// ------------------------------------------------------------------------------------------
+// b200q_gemm_nvfp4_static: the row-major-scales GEMM for callers that cannot hand in a workspace.
+//
+// Some hosts of this library have no way to obtain device memory at the moment of the call: an
+// inference server that reserved the whole GPU for its own pool at start-up (a cudaMalloc from a
+// plug-in then fails, or fragments the pool's view of the device), a real-time loop that must not
+// hit the allocator's device-wide synchronisation, or code running where the only memory it owns
+// is the operands it was given.  For them the blocked copies of the two scale arrays live in a
+// fixed array that is part of the library image, kStaticScratchBytes per GPU that loads the
+// library, held until the process exits.
+//
+//   * First call on a device: the entry point looks up the array's device address
+//     (cudaGetSymbolAddress on the symbol below; in host code the symbol's name is only a handle,
+//     never an address a kernel may be given) and caches it for that device.  Make that first
+//     call outside any stream capture.
+//   * Limit: b200q_gemm_nvfp4_workspace_bytes(M, N, K) <= kStaticScratchBytes (8 MiB: up to
+//     M = N = K = 8192); larger problems are refused with cudaErrorInvalidValue and a message on
+//     stderr.  Use b200q_gemm_nvfp4 with your own workspace for those.
+//   * One array per device, shared by every call: two calls whose kernels can overlap on the GPU
+//     (different streams, or graphs replayed concurrently) would overwrite each other's scales.
+//     Calls on one stream are safe.  Nothing in the array has to be zero beforehand: the
+//     rewrite kernel writes every byte it later reads, zero padding of ragged row blocks included,
+//     so whatever an earlier call left behind is never observed.
+//   * No allocation of any kind happens here: no cudaMalloc / cudaFree, no library call that
+//     allocates.
+
+namespace b200q {
+namespace nvfp4 {
+
+constexpr size_t kStaticScratchBytes = 8u << 20;
+static __device__ __align__(256) uint8_t g_static_sf_scratch[kStaticScratchBytes];
+
+namespace {
+std::mutex g_static_mu;
+uint8_t* g_static_ptr[64] = {};        // device address of g_static_sf_scratch, per device ordinal
+}  // namespace
+
+// Device address of the scratch array on the current device, looked up once per device.
+static cudaError_t static_scratch(uint8_t** out)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_sf_scratch);      // this device is current: its copy of the symbol
+        if (e != cudaSuccess) return e;
+        if (p == nullptr) return cudaErrorInvalidSymbol;
+        g_static_ptr[dev] = static_cast<uint8_t*>(p);
+    }
+    *out = g_static_ptr[dev];
+    return cudaSuccess;
+}
+
+}  // namespace nvfp4
+}  // namespace b200q
+
+size_t b200q_gemm_nvfp4_static_max_bytes(void) { return b200q::nvfp4::kStaticScratchBytes; }
+
+int b200q_gemm_nvfp4_static(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C, int M, int N, int K,
+                            float global_a, float global_b, void* stream)
+{
+    const size_t need = b200q_gemm_nvfp4_workspace_bytes(M, N, K);
+    if (need == 0) return cudaErrorInvalidValue;                 // bad sizes (K % 64, non-positive)
+    if (need > b200q::nvfp4::kStaticScratchBytes) {
+        std::fprintf(stderr,
+                     "b200q_gemm_nvfp4_static: M=%d N=%d K=%d needs %zu bytes of scale scratch, the built-in array holds %zu; "
+                     "use b200q_gemm_nvfp4 with a caller-owned workspace\n",
+                     M, N, K, need, b200q::nvfp4::kStaticScratchBytes);
+        return cudaErrorInvalidValue;
+    }
+    uint8_t* scratch = nullptr;
+    const cudaError_t e = b200q::nvfp4::static_scratch(&scratch);
+    if (e != cudaSuccess) return e;
+    return b200q_gemm_nvfp4(Aq, SFA, Bq, SFB, C, M, N, K, global_a, global_b, scratch, stream);
 }
 
 }  // extern "C"

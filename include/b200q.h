@@ -65,6 +65,21 @@ int b200q_gemm_nvfp4(const void* Aq, const void* SFA, const void* Bq, const void
                      int M, int N, int K, float global_a, float global_b, void* workspace, void* stream);
 size_t b200q_gemm_nvfp4_workspace_bytes(int M, int N, int K);
 
+/* b200q_gemm_nvfp4 for callers that cannot allocate.  (This entry point has no counterpart in the
+ * reference project.)  Some hosts cannot give the call a workspace: a server that handed the whole
+ * GPU to its own memory pool at start-up, a latency-critical loop that must stay clear of the
+ * allocator's device-wide synchronisation, a plug-in that owns nothing but its operands.  Here the
+ * scratch for the rewritten scales is an array inside the library image (8 MiB per GPU that loads
+ * the library, kept until exit), so the call performs no allocation of any kind.  Problems whose
+ * b200q_gemm_nvfp4_workspace_bytes(M,N,K) exceeds b200q_gemm_nvfp4_static_max_bytes() are refused
+ * with cudaErrorInvalidValue and a message on stderr (M = N = K = 8192 just fits).  The first call
+ * on a device looks up the array's device address: issue it before any stream capture.  All calls
+ * on a device share the one array — calls that may overlap on the GPU (several streams) race on
+ * it; calls on one stream are safe, and no state has to be cleared between calls. */
+int b200q_gemm_nvfp4_static(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C,
+                            int M, int N, int K, float global_a, float global_b, void* stream);
+size_t b200q_gemm_nvfp4_static_max_bytes(void);
+
 /* The same GEMM on scales that are already in the blocked layout (weights: rewrite once, reuse).
  * Blocked layout: [ceil(rows/128)][K/64] blocks of 512 bytes; inside a block the four scales of
  * row r (K-steps of 16 inside a 64-wide slab) sit at byte (r % 32) * 16 + (r / 32) * 4. */
