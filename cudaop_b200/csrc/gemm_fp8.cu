@@ -1,5 +1,6 @@
 // Host side of the FP8 GEMM entry points: argument checks, tile choice, tensor maps, launch.
 #include "gemm_fp8.cuh"
+#include "gemm_fp8_2cta.cuh"
 #include "../../include/b200q.h"
 
 namespace b200q {
@@ -9,6 +10,7 @@ namespace {
 
 int g_force_bn = 0;      // 0 = choose per problem; 224 or 256 = forced (b200q_fp8_set_tile_n)
 int g_reducer_stride = 1;
+int g_use_2cta = 1;      // 1 = CTA-pair kernel (tcgen05 cta_group::2) for the plain / row-col / SwiGLU GEMMs
 
 template <int EPI, typename OutT, int BN, bool AR>
 cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2, const Params& p,
@@ -30,6 +32,35 @@ cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
     const int grid = tiles < sms ? tiles : sms;
     kernel<<<grid, kBaseThreads + (AR ? kReducerThreads : 0), Cfg<BN>::kSmemBytes, stream>>>(tmA, tmB, tmB2, p);
     return cudaGetLastError();
+}
+
+template <int EPI, typename OutT, int BN>
+cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2, const Params& p,
+                        cudaStream_t stream)
+{
+    auto kernel = gemm_fp8_2cta_kernel<EPI, OutT, BN>;
+    constexpr int kPairSmemBytes = PairCfg<BN>::kSmemBytes;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 64 && !configured[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPairSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    const int sms = num_sms();
+    if (sms <= 0) return cudaErrorInvalidDevice;
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kBaseThreads);
+    cfg.dynamicSmemBytes = kPairSmemBytes; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmB2, p);
 }
 
 // Shared checks: pointers, positive dims, TMA constraints (16-byte aligned bases, row pitch a
@@ -109,6 +140,36 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
         if (e != cudaSuccess) return e;
     }
 
+    if (g_use_2cta && !ar) {
+        // CTA pairs: 256 x BN tiles (SwiGLU: BN/2 output columns); every CTA loads 128 rows of A and BN/2 rows of B
+        const int sms = num_sms() > 0 ? num_sms() : 148;
+        int pbn = 256; long long best = -1;
+        for (int cand : {256, 224}) {
+            if (g_force_bn && cand != g_force_bn) continue;
+            const int oc = swiglu ? cand / 2 : cand;
+            const long long tiles = static_cast<long long>((M + kPairBM - 1) / kPairBM) * ((N + oc - 1) / oc);
+            const long long cost = ((tiles + sms / 2 - 1) / (sms / 2)) * (cand + 24);
+            if (best < 0 || cost < best) { best = cost; pbn = cand; }
+        }
+        const int oc = swiglu ? pbn / 2 : pbn;
+        CUtensorMap tA, tB, tB2;
+        p.tiles_m = (M + kPairBM - 1) / kPairBM;
+        p.tiles_n = (N + oc - 1) / oc;
+        p.group = 8;
+        if (!make_tmap_2d_u8(&tA, A, M, K, K, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
+        if (!make_tmap_2d_u8(&tB, B, N, K, K, pbn / 2, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
+        tB2 = tB;
+        if (swiglu && !make_tmap_2d_u8(&tB2, B2, N, K, K, pbn / 2, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
+#define B200Q_PAIR(EPI, T) (pbn == 224 ? launch_pair<EPI, T, 224>(tA, tB, tB2, p, stream) : launch_pair<EPI, T, 256>(tA, tB, tB2, p, stream))
+        switch (epi) {
+        case kEpiTensor: return out_f32 ? B200Q_PAIR(kEpiTensor, float) : B200Q_PAIR(kEpiTensor, __nv_bfloat16);
+        case kEpiRowCol: return out_f32 ? B200Q_PAIR(kEpiRowCol, float) : B200Q_PAIR(kEpiRowCol, __nv_bfloat16);
+        case kEpiSwiGLU: return out_f32 ? cudaErrorInvalidValue : B200Q_PAIR(kEpiSwiGLU, __nv_bfloat16);
+        default: return cudaErrorInvalidValue;
+        }
+#undef B200Q_PAIR
+    }
+
     CUtensorMap tmA, tmB, tmB2;
     const uint32_t b_rows = static_cast<uint32_t>(swiglu ? bn / 2 : bn);
     if (!make_tmap_2d_u8(&tmA, A, M, K, K, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
@@ -184,6 +245,12 @@ int b200q_fp8_set_reducer_stride(int stride)
 {
     if (stride < 1 || stride > 16) return cudaErrorInvalidValue;
     b200q::fp8::g_reducer_stride = stride;
+    return 0;
+}
+
+int b200q_fp8_set_2cta(int on)
+{
+    b200q::fp8::g_use_2cta = on ? 1 : 0;
     return 0;
 }
 

@@ -99,6 +99,7 @@ int b200q_gemm_sp24_fp8(const void* Acomp, const void* Ameta, const void* B, voi
 
 /* Tuning knobs (process-wide): width of the B tile, 128 / 192 / 256 columns. */
 int b200q_fp8_set_tile_n(int bn);      /* 0 = chosen per problem (default), 224 or 256 */
+int b200q_fp8_set_2cta(int on);        /* FP8 GEMMs on CTA pairs (tcgen05 cta_group::2, 256-row tiles); default on */
 int b200q_fp8_set_reducer_stride(int stride);   /* fused all-reduce: every stride-th CTA reduces, 1..16 */
 int b200q_nvfp4_set_tile_n(int bn);
 int b200q_w4a16_set_impl(int impl);     /* 0 = warp-MMA kernel (default, measured faster), 1 = tcgen05 kernel */

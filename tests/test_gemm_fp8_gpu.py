@@ -11,6 +11,15 @@ from tests.util import CORES, assert_bar, bf16_to_f32, dev
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[1, 0], ids=["cta_pair", "one_cta"], autouse=True)
+def kernel_variant(request):
+    """Both FP8 kernels: CTA pairs (tcgen05 cta_group::2, default) and the one-CTA kernel."""
+    import cudaop_b200 as ops
+    ops.lib().b200q_fp8_set_2cta(request.param)
+    yield request.param
+    ops.lib().b200q_fp8_set_2cta(1)
+
+
 def _run(aq, bq, sa, sb):
     import cudaop_b200 as ops
     out = ops.gemm_fp8(dev(aq), dev(bq), sa, sb)
