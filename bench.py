@@ -44,47 +44,81 @@ def measured_peaks() -> dict:
 # ------------------------------------------------------------------------- clocks
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples SM clock, power and throttle reasons while the timed region runs (read-only NVML
+    queries every few milliseconds; nvidia-smi polling as the fallback)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
          "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.stop_flag, self.thread = index, [], None, False, None
+        self.nvml = None
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[self.index]) if vis and vis.split(",")[self.index].isdigit() else self.index
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.nvml = pynvml
+            self.max_sm = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.thread = threading.Thread(target=self._poll, daemon=True); self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=self._read, daemon=True); self.t.start()
+            self.thread = threading.Thread(target=self._read, daemon=True); self.thread.start()
         except Exception:
             self.proc = None
 
+    def _poll(self):
+        n = self.nvml
+        names = {"hw_slowdown": n.nvmlClocksThrottleReasonHwSlowdown,
+                 "hw_thermal_slowdown": n.nvmlClocksThrottleReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": n.nvmlClocksThrottleReasonSwThermalSlowdown,
+                 "sw_power_cap": n.nvmlClocksThrottleReasonSwPowerCap}
+        while not self.stop_flag:
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                pw = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                rs = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.rows.append((float(sm), float(self.max_sm), pw, [k for k, bit in names.items() if rs & bit]))
+            except Exception:
+                pass
+            time.sleep(0.004)
+
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            pass
-        sm, mx, reasons, pw = [], [], set(), []
-        for r in self.rows:
+            r = [c.strip() for c in line.split(",")]
             try:
-                sm.append(float(r[1])); mx.append(float(r[2])); pw.append(float(r[3]))
-                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
-                    if v.lower().startswith("active"):
-                        reasons.add(name)
+                reasons = [nm for nm, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9])
+                           if v.lower().startswith("active")]
+                self.rows.append((float(r[1]), float(r[2]), float(r[3]), reasons))
             except Exception:
                 continue
-        hi = [s for s, p in zip(sm, pw) if p >= 0.5 * max(pw)] if pw else sm
-        return {"sm_mhz": statistics.median(hi) if hi else None, "sm_max_mhz": max(mx) if mx else None,
-                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+    def stop(self) -> dict:
+        self.stop_flag = True
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        pw = [r[2] for r in self.rows]
+        busy = [r for r in self.rows if r[2] >= 0.6 * max(pw)] or self.rows      # samples taken under load
+        reasons = sorted({x for r in busy for x in r[3]})
+        return {"sm_mhz": statistics.median(r[0] for r in busy), "sm_max_mhz": max(r[1] for r in self.rows),
+                "power_w_max": max(pw), "samples": len(self.rows), "samples_under_load": len(busy),
+                "reasons": reasons, "source": "nvml" if self.nvml else "nvidia-smi"}
 
 
 # ------------------------------------------------------------------ CPU reference arm
@@ -210,6 +244,27 @@ def gemm_cases(peaks):
     out["fp8_8192"] = {"ms": ms, "tflops": tf, "frac_nominal_4500": tf / NOMINAL["fp8_tflops"],
                        "frac_2x_measured_bf16": tf / fp8_meas}
     del a, b, c
+    # NVFP4 8192^3 (scales pre-blocked, as weights would be)
+    A4 = torch.randint(0, 256, (S, S // 2), dtype=torch.uint8, device="cuda")
+    B4 = torch.randint(0, 256, (S, S // 2), dtype=torch.uint8, device="cuda")
+    sf = torch.randint(0x28, 0x48, (L.b200q_nvfp4_sf_bytes(S, S),), dtype=torch.uint8, device="cuda")
+    c = torch.empty((S, S), dtype=torch.bfloat16, device="cuda")
+    ms = time_loop(lambda: L.b200q_gemm_nvfp4_blocked(A4.data_ptr(), sf.data_ptr(), B4.data_ptr(), sf.data_ptr(), c.data_ptr(),
+                                                      S, S, S, 1.0, 1.0, st()), 20)
+    tf = 2 * S ** 3 / ms / 1e9
+    out["nvfp4_8192"] = {"ms": ms, "tflops": tf, "frac_nominal_9000": tf / NOMINAL["fp4_tflops"],
+                         "frac_4x_measured_bf16": tf / (4.0 * peaks["bf16_tflops"])}
+    del A4, B4, sf
+    # 2:4 sparse FP8 4096 x 8192 x 8192 (dense-equivalent FLOPs)
+    Ms = 4096
+    Ac = torch.randint(0, 120, (Ms, S // 2), dtype=torch.uint8, device="cuda")
+    Em = torch.full((Ms, S // 8), 0xE4, dtype=torch.uint8, device="cuda")
+    Bd = torch.randint(0, 120, (S, S), dtype=torch.uint8, device="cuda")
+    ms = time_loop(lambda: L.b200q_gemm_sp24_fp8(Ac.data_ptr(), Em.data_ptr(), Bd.data_ptr(), c.data_ptr(), Ms, S, S, 1.0, 1.0, st()), 20)
+    tf = 2 * Ms * S * S / ms / 1e9
+    out["sparse_fp8_4096x8192x8192"] = {"ms": ms, "tflops_dense_equivalent": tf, "frac_nominal_dense_4500": tf / NOMINAL["fp8_tflops"],
+                                        "frac_nominal_sparse_9000": tf / (2 * NOMINAL["fp8_tflops"])}
+    del Ac, Em, Bd, c
     # W4A16 decode: 80 distinct weight sets (671 MB > L2) cycled inside one CUDA graph
     N = K = 4096
     nsets = 80

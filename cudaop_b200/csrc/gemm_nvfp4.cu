@@ -35,15 +35,21 @@ constexpr uint32_t kTmemCols = 512;
 
 template <int BN>
 struct Cfg {
-    static constexpr int kNB = (BN + 127) / 128;                    // scale row-blocks per B tile (of 128 rows)
+    // scale row-blocks (of 128 rows) a B tile can span: tiles start at multiples of BN, so at offset
+    // 0 or 64 inside their first block.  BN must be a multiple of 64: the tensor core takes the B
+    // scales from a TMEM address that is a multiple of two columns (64 rows of B); a 224-wide tile,
+    // whose odd tiles start 32 or 96 rows into a block, raised "misaligned address".
+    static_assert(BN % 64 == 0, "B tile width must be a multiple of 64 for the scale-factor address");
+    static constexpr int kMaxOff = (BN % 128 == 0) ? 0 : 64;
+    static constexpr int kNB = (kMaxOff + BN + 127) / 128;
     static constexpr int kABytes = kBM * kBKBytes;                  // 16 KiB
     static constexpr int kBBytes = BN * kBKBytes;
     static constexpr int kSfaBytes = 4 * kSfBlockBytes;             // 4 K-steps
     static constexpr int kSfbBytes = kNB * 4 * kSfBlockBytes;
     static constexpr int kStageBytes = kABytes + kBBytes + kSfaBytes + kSfbBytes;   // multiple of 1024
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
-    static constexpr int kSfaCol = 2 * BN <= 384 ? 2 * BN : BN;     // first scale column in TMEM
-    static constexpr int kAccBufs = 2 * BN <= 384 ? 2 : 1;
+    static constexpr int kAccBufs = (2 * BN + 16 + 16 * kNB <= 512) ? 2 : 1;   // two accumulators when they fit beside the scales
+    static constexpr int kSfaCol = kAccBufs * BN;                   // first scale column in TMEM
     static constexpr int kSfbCol = kSfaCol + 16;
     static_assert(kSfbCol + 4 * 4 * kNB <= 512, "TMEM budget");
     static_assert(kStageBytes % 1024 == 0, "stage alignment");
