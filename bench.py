@@ -328,7 +328,7 @@ def run_ours(args):
     sg = rand_scale(loc, 4000 + rank); su = rand_scale(loc, 5000 + rank); sd = rand_scale(HIDDEN, 6000)
     mlp = TensorParallelMLP(wg, sg, wu, su, wd, sd, rank=rank, world=world, device=dev, max_tokens=TOKENS,
                             chunks=args.chunks if world > 1 else 1, presharded=True, comm=args.comm,
-                            ar_ctas=args.ar_ctas, use_multicast=args.multicast,
+                            ar_ctas=args.ar_ctas, use_multicast={"auto": None, "on": True, "off": False}[args.multicast],
                             partial_dtype=torch.float32 if args.partial == "fp32" else torch.bfloat16)
     del wg, wu, wd
 
@@ -386,7 +386,7 @@ def run_ours(args):
     # ---- latency of ONE forward with nothing else in flight (N > 1: the fused GEMM + all-reduce kernel)
     if world > 1:
         lat = TensorParallelMLP(mlp.wg, mlp.sg, mlp.wu, mlp.su, mlp.wd, mlp.sd, rank=rank, world=world, device=dev,
-                                max_tokens=TOKENS, presharded=True, comm="fused", use_multicast=args.multicast,
+                                max_tokens=TOKENS, presharded=True, comm="fused", use_multicast=mlp.use_multicast,
                                 partial_dtype=mlp.partial_dtype)
         ms_latency = timed(lambda: lat.forward(x), args.steps, args.warmup)
     else:
@@ -475,9 +475,10 @@ def main():
     ap.add_argument("--chunks", type=int, default=4, help="token chunks for all-reduce overlap (N > 1)")
     ap.add_argument("--comm", default="pipelined", choices=["auto", "pipelined", "fused", "symm", "nccl"],
                     help="all-reduce: the library's NVSwitch kernel over symmetric memory, or NCCL")
-    ap.add_argument("--ar-ctas", type=int, default=64)
+    ap.add_argument("--ar-ctas", type=int, default=32)
     ap.add_argument("--partial", default="bf16", choices=["bf16", "fp32"], help="dtype of the partial outputs that cross NVLink")
-    ap.add_argument("--multicast", action="store_true", help="reduce and broadcast in the NVSwitch (multimem) instead of peer loads/stores")
+    ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"],
+                    help="reduce and broadcast in the NVSwitch (multimem) instead of peer loads/stores; auto = from 4 ranks on")
     ap.add_argument("--cpu-tokens", type=int, default=64, help="tokens in the CPU-baseline sample")
     ap.add_argument("--no-cases", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

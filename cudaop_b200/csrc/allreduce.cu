@@ -97,7 +97,7 @@ allreduce_to_bf16_kernel(const Params p)
 }
 
 int g_unroll = 4;
-int g_threads = 512;
+int g_threads = 256;
 
 }  // namespace ar
 }  // namespace b200q

@@ -1,7 +1,7 @@
 // Activation quantiser: bf16 rows -> E4M3 bytes + one fp32 scale per row (token).
 //   s[r] = max|x[r,:]| / 448  (1.0 for an all-zero row),  q = e4m3_rn_satfinite(x / s[r])
-// Bandwidth-bound: one CTA per row, 16-byte loads, row maximum by warp shuffles + shared
-// memory, second pass re-reads the row (an L2 hit) and writes 8 bytes per 8 inputs.
+// Bandwidth-bound: one CTA per row, 16-byte streaming loads held in registers across the two
+// passes (row maximum by warp shuffles + shared memory, then convert), 8 bytes written per 8 inputs.
 #include "common.cuh"
 #include <cuda_fp8.h>
 #include "../../include/b200q.h"
@@ -21,7 +21,12 @@ __device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d
     return lo | (hi << 16);
 }
 
-__global__ void __launch_bounds__(kThreads)
+// One CTA per row.  Every thread keeps its share of the row (up to kCache 16-byte vectors = 112
+// values) in registers between the maximum pass and the convert pass, so a row is read from memory
+// once; all of a thread's loads are issued before the first is used.  Longer rows re-read the rest.
+constexpr int kCache = 14;
+
+__global__ void __launch_bounds__(kThreads, 2)
 quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict__ Q, float* __restrict__ S, int rows,
                        int cols)
 {
@@ -30,12 +35,24 @@ quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict_
     const int vecs = cols / 8;
     for (int row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint4* x = reinterpret_cast<const uint4*>(X + static_cast<size_t>(row) * cols);
+        uint4 cache[kCache];
+#pragma unroll
+        for (int i = 0; i < kCache; ++i) {
+            const int v = threadIdx.x + i * kThreads;
+            cache[i] = (v < vecs) ? __ldcs(x + v) : make_uint4(0, 0, 0, 0);
+        }
         float mx = 0.0f;
-        for (int v = threadIdx.x; v < vecs; v += kThreads) {
+#pragma unroll
+        for (int i = 0; i < kCache; ++i) {
+            const uint32_t w[4] = {cache[i].x, cache[i].y, cache[i].z, cache[i].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) mx = fmaxf(mx, fmaxf(fabsf(bf16_lo(w[k])), fabsf(bf16_hi(w[k]))));
+        }
+        for (int v = threadIdx.x + kCache * kThreads; v < vecs; v += kThreads) {      // rows longer than the cache
             const uint4 u = __ldg(x + v);
             const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) mx = fmaxf(mx, fmaxf(fabsf(bf16_lo(w[i])), fabsf(bf16_hi(w[i]))));
+            for (int k = 0; k < 4; ++k) mx = fmaxf(mx, fmaxf(fabsf(bf16_lo(w[k])), fabsf(bf16_hi(w[k]))));
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
@@ -51,15 +68,20 @@ quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict_
         __syncthreads();
         const float sc = s_scale;
         uint2* q = reinterpret_cast<uint2*>(Q + static_cast<size_t>(row) * cols);
-        for (int v = threadIdx.x; v < vecs; v += kThreads) {
-            const uint4 u = __ldg(x + v);
+        auto convert = [&](uint4 u) {
             uint2 o;
             o.x = cvt4_e4m3(__fdiv_rn(bf16_lo(u.x), sc), __fdiv_rn(bf16_hi(u.x), sc), __fdiv_rn(bf16_lo(u.y), sc),
                             __fdiv_rn(bf16_hi(u.y), sc));
             o.y = cvt4_e4m3(__fdiv_rn(bf16_lo(u.z), sc), __fdiv_rn(bf16_hi(u.z), sc), __fdiv_rn(bf16_lo(u.w), sc),
                             __fdiv_rn(bf16_hi(u.w), sc));
-            q[v] = o;
+            return o;
+        };
+#pragma unroll
+        for (int i = 0; i < kCache; ++i) {
+            const int v = threadIdx.x + i * kThreads;
+            if (v < vecs) q[v] = convert(cache[i]);
         }
+        for (int v = threadIdx.x + kCache * kThreads; v < vecs; v += kThreads) q[v] = convert(__ldg(x + v));
         __syncthreads();
     }
 }
