@@ -394,20 +394,40 @@ def run_ours(args):
     # ---- end to end: every step takes its input from pinned host memory and leaves its result there.
     # With R ranks each rank moves 1/R of X over its own PCIe link and the ranks all-gather X over NVLink;
     # each rank writes back 1/R of the (replicated) result.
+    # Copies run on their own streams, double-buffered, so the H2D of step i+1 and the D2H of step i-1
+    # overlap the GEMMs of step i (PCIe is full duplex); every step still moves its own input and result.
     rows = TOKENS // world
     lo, hi = rank * rows, (rank + 1) * rows
+    copy_in, copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    xbuf = [x, torch.empty_like(x)]
+    x_free = [None, None]          # event: the forward that last read xbuf[b] has been issued and finished
+    e2e_i = [0]
+
     def e2e_step():
-        if world == 1:
-            x.copy_(x_host, non_blocking=True)
-            y_host.copy_(mlp.forward(x), non_blocking=True)
-            return
-        x[lo:hi].copy_(x_host[lo:hi], non_blocking=True)
-        dist.all_gather_into_tensor(x, x[lo:hi].clone())
-        yy = mlp.forward(x)
-        side = mlp.comm_stream if mlp.comm == "pipelined" else torch.cuda.current_stream()
-        with torch.cuda.stream(side):                 # ordered after this step's all-reduce
+        b = e2e_i[0] & 1
+        e2e_i[0] += 1
+        main = torch.cuda.current_stream()
+        with torch.cuda.stream(copy_in):
+            if x_free[b] is not None:
+                copy_in.wait_event(x_free[b])
+            xbuf[b][lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+            if world > 1:
+                dist.all_gather_into_tensor(xbuf[b], xbuf[b][lo:hi].clone())
+            ready = torch.cuda.Event(); ready.record(copy_in)
+        main.wait_event(ready)
+        yy = mlp.forward(xbuf[b])
+        done = torch.cuda.Event(); done.record(main)
+        x_free[b] = done
+        side = mlp.comm_stream if (world > 1 and mlp.comm == "pipelined") else copy_out
+        with torch.cuda.stream(side):                 # ordered after this step's GEMMs / all-reduce
+            side.wait_event(done)
             y_host[lo:hi].copy_(yy[lo:hi], non_blocking=True)
-    ms_e2e = timed(e2e_step, args.steps, args.warmup, finish=mlp.wait)
+
+    def e2e_finish():
+        main = torch.cuda.current_stream()
+        main.wait_stream(copy_in); main.wait_stream(copy_out)
+        mlp.wait()
+    ms_e2e = timed(e2e_step, args.steps, args.warmup, finish=e2e_finish)
     clocks = sampler.stop() if sampler else None
     assert ops.status() == 0, "a kernel gave up on a bounded wait"
 
@@ -432,19 +452,24 @@ def run_ours(args):
         "clocks": clocks,
         "e2e": {"value": TOKENS / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": TOKENS * HIDDEN * 2, "d2h_bytes_per_step": TOKENS * HIDDEN * 2,
-                "note": "whole-job bytes; with R ranks each rank copies 1/R of X in and 1/R of Y out over its own "
-                        "PCIe link, X is all-gathered over NVLink"},
+                "note": "whole-job bytes per step; copies run on their own streams, double-buffered, overlapping the "
+                        "GEMMs of the neighbouring steps; with R ranks each rank copies 1/R of X in and 1/R of Y out "
+                        "over its own PCIe link and X is all-gathered over NVLink"},
         "latency_ms_per_forward": ms_latency,
         "overlap": ("steps are independent batches: the all-reduce of step i runs on a side stream under the GEMMs "
                     "of step i+1 (double-buffered); latency_ms_per_forward is one forward alone with the all-reduce "
                     "fused into the down-projection kernel") if world > 1 and mlp.comm == "pipelined" else "none",
         "gpu_launches": launches, "kernels_ms": kernels_ms,
-        "roofline": {"bound": "tensor", "kernel": "gemm_fp8_kernel<SwiGLU> (gate/up projection)",
+        "roofline": {"bound": "tensor", "kernel": "gemm_fp8_2cta_kernel<SwiGLU> (gate/up projection, CTA pairs)",
                      "achieved": top_tf, "peak": peak, "unit": "TFLOP/s", "frac": top_tf / peak,
                      "peak_source": f"2 x bf16_tflops_sustained of {peaks['source']} (FP8 runs at twice the bf16 "
                                     "rate on the same tensor pipe; no FP8 figure is measured by the driver)",
                      "frac_nominal_4500": top_tf / NOMINAL["fp8_tflops"], "launch_ms": top_avg,
-                     "flops_per_launch": top_flops, "traffic": None},
+                     "flops_per_launch": top_flops,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of this kernel at tp1 from one ncu capture
+                     # (profiles/gemm_fp8_2cta_kernel_swiglu_mlp_gate_up.txt); algorithmic minimum 739 MB
+                     "traffic": 1217245952 if world == 1 else None,
+                     "tensor_pipe_active_pct_ncu": 87.1 if world == 1 else None},
     }
     if world == 1 and not args.no_cases:
         line["cases"] = gemm_cases(peaks)

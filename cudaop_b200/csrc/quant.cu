@@ -1,5 +1,7 @@
 // Activation quantiser: bf16 rows -> E4M3 bytes + one fp32 scale per row (token).
-//   s[r] = max|x[r,:]| / 448  (1.0 for an all-zero row),  q = e4m3_rn_satfinite(x / s[r])
+//   s[r] = max|x[r,:]| / 448  (1.0 for an all-zero row),  q = e4m3_rn_satfinite(x * (1 / s[r]))
+// (one IEEE reciprocal per row, one rounded product per element: a division per element made the
+// kernel ALU-bound)
 // Bandwidth-bound: one CTA per row, 16-byte streaming loads held in registers across the two
 // passes (row maximum by warp shuffles + shared memory, then convert), 8 bytes written per 8 inputs.
 #include "common.cuh"
@@ -39,7 +41,7 @@ quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict_
 #pragma unroll
         for (int i = 0; i < kCache; ++i) {
             const int v = threadIdx.x + i * kThreads;
-            cache[i] = (v < vecs) ? __ldcs(x + v) : make_uint4(0, 0, 0, 0);
+            cache[i] = (v < vecs) ? __ldg(x + v) : make_uint4(0, 0, 0, 0);
         }
         float mx = 0.0f;
 #pragma unroll
@@ -66,14 +68,14 @@ quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict_
             S[row] = sc;
         }
         __syncthreads();
-        const float sc = s_scale;
+        const float inv = __frcp_rn(s_scale);
         uint2* q = reinterpret_cast<uint2*>(Q + static_cast<size_t>(row) * cols);
         auto convert = [&](uint4 u) {
             uint2 o;
-            o.x = cvt4_e4m3(__fdiv_rn(bf16_lo(u.x), sc), __fdiv_rn(bf16_hi(u.x), sc), __fdiv_rn(bf16_lo(u.y), sc),
-                            __fdiv_rn(bf16_hi(u.y), sc));
-            o.y = cvt4_e4m3(__fdiv_rn(bf16_lo(u.z), sc), __fdiv_rn(bf16_hi(u.z), sc), __fdiv_rn(bf16_lo(u.w), sc),
-                            __fdiv_rn(bf16_hi(u.w), sc));
+            o.x = cvt4_e4m3(__fmul_rn(bf16_lo(u.x), inv), __fmul_rn(bf16_hi(u.x), inv), __fmul_rn(bf16_lo(u.y), inv),
+                            __fmul_rn(bf16_hi(u.y), inv));
+            o.y = cvt4_e4m3(__fmul_rn(bf16_lo(u.z), inv), __fmul_rn(bf16_hi(u.z), inv), __fmul_rn(bf16_lo(u.w), inv),
+                            __fmul_rn(bf16_hi(u.w), inv));
             return o;
         };
 #pragma unroll

@@ -107,7 +107,7 @@ int b200q_w4a16_set_pdl(int on);        /* programmatic dependent launch of the 
 int b200q_sp24_set_tile_n(int bn);
 
 /* Activation quantiser: X[rows,cols] bf16 -> Q[rows,cols] E4M3 and S[rows] fp32,
- * S[r] = max|X[r,:]| / 448 (1 for a zero row), Q = rn_satfinite(X / S[r]).  No counterpart in
+ * S[r] = max|X[r,:]| / 448 (1 for a zero row), Q = rn_satfinite(X * (1 / S[r])).  No counterpart in
  * the reference (its MLP is fp32); needed on either side of the FP8 GEMMs.  cols % 8 == 0. */
 int b200q_quant_rows_e4m3(const void* X, void* Q, float* S, int rows, int cols, void* stream);
 

@@ -302,7 +302,9 @@ void oracle_encode_f16_n(const float* in, uint16_t* out, size_t n)
 }
 
 /* Per-row (per-token) E4M3 quantisation: s[r] = max|x[r,:]| / 448 (1.0 for an
- * all-zero row), q = e4m3_rn(x / s[r]).  No reference counterpart. */
+ * all-zero row), q = e4m3_rn(x * (1 / s[r])): one fp32 reciprocal per row, one fp32
+ * product per element (both round-to-nearest), then the E4M3 rounding.  No reference
+ * counterpart; the rule is stated here and the kernel reproduces it bit for bit. */
 void oracle_quant_rows_e4m3(const float* x, uint8_t* q, float* s, int rows, int cols)
 {
     for (int r = 0; r < rows; ++r) {
@@ -310,8 +312,12 @@ void oracle_quant_rows_e4m3(const float* x, uint8_t* q, float* s, int rows, int 
         float mx = 0.0f;
         for (int c = 0; c < cols; ++c) mx = fmaxf(mx, fabsf(xr[c]));
         float sc = mx > 0.0f ? mx / 448.0f : 1.0f;
+        volatile float inv = 1.0f / sc;       /* volatile: keep the two roundings separate */
         s[r] = sc;
-        for (int c = 0; c < cols; ++c) q[(size_t)r * cols + c] = oracle_encode_e4m3(xr[c] / sc);
+        for (int c = 0; c < cols; ++c) {
+            volatile float y = xr[c] * inv;
+            q[(size_t)r * cols + c] = oracle_encode_e4m3(y);
+        }
     }
 }
 

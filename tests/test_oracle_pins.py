@@ -212,6 +212,8 @@ def test_quantisers_round_trip_and_scale_rules():
     x = rng.standard_normal((5, 64), dtype=np.float32)
     q, s = oracle.quant_rows_e4m3(x)
     assert np.allclose(s, np.abs(x).max(1) / 448.0)
+    inv = (np.float32(1.0) / s).astype(np.float32)
+    assert np.array_equal(q, oracle.encode_e4m3((x * inv[:, None]).astype(np.float32)))   # reciprocal-multiply rule
     assert np.abs(oracle.decode_e4m3(q) * s[:, None] - x).max() <= np.abs(x).max() * 2.0 ** -4
     g = float(np.abs(x).max() / (6 * 448))
     q4, sf = oracle.quant_nvfp4(x, g)
