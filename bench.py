@@ -500,7 +500,7 @@ def main():
     ap.add_argument("--chunks", type=int, default=4, help="token chunks for all-reduce overlap (N > 1)")
     ap.add_argument("--comm", default="pipelined", choices=["auto", "pipelined", "fused", "symm", "nccl"],
                     help="all-reduce: the library's NVSwitch kernel over symmetric memory, or NCCL")
-    ap.add_argument("--ar-ctas", type=int, default=32)
+    ap.add_argument("--ar-ctas", type=int, default=None, help="CTAs of the stand-alone all-reduce kernel (default: by transport)")
     ap.add_argument("--partial", default="bf16", choices=["bf16", "fp32"], help="dtype of the partial outputs that cross NVLink")
     ap.add_argument("--multicast", default="auto", choices=["auto", "on", "off"],
                     help="reduce and broadcast in the NVSwitch (multimem) instead of peer loads/stores; auto = from 4 ranks on")

@@ -55,7 +55,7 @@ class TensorParallelMLP:
 
     def __init__(self, w_gate, s_gate, w_up, s_up, w_down, s_down, rank: int = 0, world: int = 1,
                  group=None, device=None, max_tokens: int = 4096, chunks: int | None = None,
-                 presharded: bool = False, comm: str = "auto", ar_ctas: int = 32, partial_dtype=torch.bfloat16,
+                 presharded: bool = False, comm: str = "auto", ar_ctas: int | None = None, partial_dtype=torch.bfloat16,
                  use_multicast: bool | None = None):
         self.rank, self.world, self.group = rank, world, group
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
@@ -137,6 +137,18 @@ class TensorParallelMLP:
         self._hy = symm.rendezvous(self._y_all, group)
         self._hf = symm.rendezvous(self.flags, group)
         self.multicast = self.use_multicast and bool(self._hp.multicast_ptr) and bool(self._hy.multicast_ptr)
+        # launch shape of the stand-alone all-reduce kernel, from measurements at 2/4/8 ranks: the
+        # in-switch reduction saturates with few threads (and then disturbs a co-running GEMM least),
+        # peer loads need many requests in flight from every SM
+        L = ops.lib()
+        if self.multicast:
+            L.b200q_allreduce_set_threads(256); L.b200q_allreduce_set_unroll(4)
+            if self.ar_ctas is None:
+                self.ar_ctas = 32
+        else:
+            L.b200q_allreduce_set_threads(128); L.b200q_allreduce_set_unroll(8)
+            if self.ar_ctas is None:
+                self.ar_ctas = 148
         torch.cuda.synchronize(dev)
         dist.barrier(group=group)
 
