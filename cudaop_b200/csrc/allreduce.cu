@@ -98,6 +98,7 @@ allreduce_to_bf16_kernel(const Params p)
 
 int g_unroll = 4;
 int g_threads = 256;
+int g_reserved_smem = 0;   // dynamic shared memory requested only to keep the CTAs off SMs that host a GEMM CTA
 
 }  // namespace ar
 }  // namespace b200q
@@ -132,7 +133,13 @@ int b200q_allreduce_to_bf16(const void* const* partial_ptrs_dev, void* const* ou
     if (p.status == nullptr) return cudaErrorInvalidDevice;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool mc = partial_multicast != nullptr;
-#define B200Q_AR(MC_, BF_, U_) ar::allreduce_to_bf16_kernel<MC_, BF_, U_><<<ctas, ar::g_threads, 0, s>>>(p)
+#define B200Q_AR(MC_, BF_, U_)                                                                                   \
+    do {                                                                                                        \
+        if (ar::g_reserved_smem > 48 * 1024)                                                                    \
+            cudaFuncSetAttribute(ar::allreduce_to_bf16_kernel<MC_, BF_, U_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 ar::g_reserved_smem);                                                          \
+        ar::allreduce_to_bf16_kernel<MC_, BF_, U_><<<ctas, ar::g_threads, ar::g_reserved_smem, s>>>(p);          \
+    } while (0)
 #define B200Q_AR_U(MC_, BF_) do { if (ar::g_unroll >= 8) B200Q_AR(MC_, BF_, 8); else if (ar::g_unroll >= 4) B200Q_AR(MC_, BF_, 4); else if (ar::g_unroll >= 2) B200Q_AR(MC_, BF_, 2); else B200Q_AR(MC_, BF_, 1); } while (0)
     if (partial_is_bf16) { if (mc) B200Q_AR_U(true, true); else B200Q_AR_U(false, true); }
     else { if (mc) B200Q_AR_U(true, false); else B200Q_AR_U(false, false); }
@@ -145,6 +152,13 @@ int b200q_allreduce_set_unroll(int unroll)
 {
     if (unroll < 1 || unroll > 8) return cudaErrorInvalidValue;
     b200q::ar::g_unroll = unroll;
+    return 0;
+}
+
+int b200q_allreduce_set_reserved_smem(int bytes)
+{
+    if (bytes < 0 || bytes > 200 * 1024) return cudaErrorInvalidValue;
+    b200q::ar::g_reserved_smem = bytes;
     return 0;
 }
 

@@ -10,6 +10,13 @@ namespace {
 
 int g_force_bn = 0;      // 0 = choose per problem; 224 or 256 = forced (b200q_fp8_set_tile_n)
 int g_reducer_stride = 1;
+int g_sm_limit = 0;       // 0 = all SMs; otherwise the persistent grids use at most this many (b200q_fp8_set_sm_limit)
+
+int usable_sms()
+{
+    const int n = num_sms();
+    return (g_sm_limit > 0 && g_sm_limit < n) ? g_sm_limit : n;
+}
 int g_use_2cta = 1;      // 1 = CTA-pair kernel (tcgen05 cta_group::2) for the plain / row-col / SwiGLU GEMMs
 
 template <int EPI, typename OutT, int BN, bool AR>
@@ -26,7 +33,7 @@ cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    const int sms = num_sms();
+    const int sms = usable_sms();
     if (sms <= 0) return cudaErrorInvalidDevice;
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sms ? tiles : sms;
@@ -49,7 +56,7 @@ cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    const int sms = num_sms();
+    const int sms = usable_sms();
     if (sms <= 0) return cudaErrorInvalidDevice;
     const int tiles = p.tiles_m * p.tiles_n;
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
@@ -79,7 +86,7 @@ bool bad_operands(const void* A, const void* B, const void* C, int M, int N, int
 int choose_bn(int M, int n_out, bool swiglu)
 {
     if (g_force_bn) return g_force_bn;
-    const int sms = num_sms() > 0 ? num_sms() : 148;
+    const int sms = usable_sms() > 0 ? usable_sms() : 148;
     long long best_cost = -1; int best = 256;
     for (int bn : {256, 224}) {
         const int out_cols = swiglu ? bn / 2 : bn;
@@ -142,7 +149,7 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
 
     if (g_use_2cta && !ar) {
         // CTA pairs: 256 x BN tiles (SwiGLU: BN/2 output columns); every CTA loads 128 rows of A and BN/2 rows of B
-        const int sms = num_sms() > 0 ? num_sms() : 148;
+        const int sms = usable_sms() > 0 ? usable_sms() : 148;
         int pbn = 256; long long best = -1;
         for (int cand : {256, 224}) {
             if (g_force_bn && cand != g_force_bn) continue;
@@ -245,6 +252,13 @@ int b200q_fp8_set_reducer_stride(int stride)
 {
     if (stride < 1 || stride > 16) return cudaErrorInvalidValue;
     b200q::fp8::g_reducer_stride = stride;
+    return 0;
+}
+
+int b200q_fp8_set_sm_limit(int sms)
+{
+    if (sms < 0) return cudaErrorInvalidValue;
+    b200q::fp8::g_sm_limit = sms;
     return 0;
 }
 

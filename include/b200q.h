@@ -99,6 +99,11 @@ int b200q_gemm_sp24_fp8(const void* Acomp, const void* Ameta, const void* B, voi
 
 /* Tuning knobs (process-wide): width of the B tile, 128 / 192 / 256 columns. */
 int b200q_fp8_set_tile_n(int bn);      /* 0 = chosen per problem (default), 224 or 256 */
+/* SM partitioning for overlapping the stand-alone all-reduce with GEMMs: the persistent FP8 grids use at
+ * most `sms` SMs (0 = all), and the all-reduce kernel asks for `bytes` of shared memory it does not use, so its
+ * CTAs cannot share an SM with a GEMM CTA and land on the SMs left free. */
+int b200q_fp8_set_sm_limit(int sms);
+int b200q_allreduce_set_reserved_smem(int bytes);
 int b200q_fp8_set_2cta(int on);        /* FP8 GEMMs on CTA pairs (tcgen05 cta_group::2, 256-row tiles); default on */
 int b200q_fp8_set_reducer_stride(int stride);   /* fused all-reduce: every stride-th CTA reduces, 1..16 */
 int b200q_nvfp4_set_tile_n(int bn);
