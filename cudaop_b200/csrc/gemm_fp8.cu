@@ -17,6 +17,7 @@ int usable_sms()
     const int n = num_sms();
     return (g_sm_limit > 0 && g_sm_limit < n) ? g_sm_limit : n;
 }
+int g_tma_store = 1;     // CTA-pair kernels: bf16 results through shared memory + TMA stores (0: per-thread 16-byte stores)
 int g_use_2cta = 1;      // 1 = CTA-pair kernel (tcgen05 cta_group::2) for the plain / row-col / SwiGLU GEMMs
 
 template <int EPI, typename OutT, int BN, bool AR>
@@ -42,8 +43,8 @@ cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
 }
 
 template <int EPI, typename OutT, int BN>
-cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2, const Params& p,
-                        cudaStream_t stream)
+cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2, const CUtensorMap& tmC,
+                        const Params& p, cudaStream_t stream)
 {
     auto kernel = gemm_fp8_2cta_kernel<EPI, OutT, BN>;
     constexpr int kPairSmemBytes = PairCfg<BN>::kSmemBytes;
@@ -67,7 +68,7 @@ cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CU
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmB2, p);
+    return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmB2, tmC, p);
 }
 
 // Shared checks: pointers, positive dims, TMA constraints (16-byte aligned bases, row pitch a
@@ -167,7 +168,20 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
         if (!make_tmap_2d_u8(&tB, B, N, K, K, pbn / 2, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
         tB2 = tB;
         if (swiglu && !make_tmap_2d_u8(&tB2, B2, N, K, K, pbn / 2, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
-#define B200Q_PAIR(EPI, T) (pbn == 224 ? launch_pair<EPI, T, 224>(tA, tB, tB2, p, stream) : launch_pair<EPI, T, 256>(tA, tB, tB2, p, stream))
+        // bf16 results: the output as a tensor map with the epilogue's 32-row x (32- or 16-column) boxes
+        CUtensorMap tC = tA;
+        p.tma_store = 0;
+        if (!out_f32 && g_tma_store && (ldc * 2) % 16 == 0 && aligned16(C)) {
+            const uint32_t cw = (oc % 32 == 0) ? 32u : 16u;
+            const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
+            const uint64_t strides[1] = {static_cast<uint64_t>(ldc) * 2};
+            const uint32_t box[2] = {cw, 32};
+            if (encode_tiled(&tC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dims, strides, box,
+                             cw == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B) != CUDA_SUCCESS)
+                return cudaErrorInvalidValue;
+            p.tma_store = 1;
+        }
+#define B200Q_PAIR(EPI, T) (pbn == 224 ? launch_pair<EPI, T, 224>(tA, tB, tB2, tC, p, stream) : launch_pair<EPI, T, 256>(tA, tB, tB2, tC, p, stream))
         switch (epi) {
         case kEpiTensor: return out_f32 ? B200Q_PAIR(kEpiTensor, float) : B200Q_PAIR(kEpiTensor, __nv_bfloat16);
         case kEpiRowCol: return out_f32 ? B200Q_PAIR(kEpiRowCol, float) : B200Q_PAIR(kEpiRowCol, __nv_bfloat16);
@@ -265,6 +279,12 @@ int b200q_fp8_set_sm_limit(int sms)
 int b200q_fp8_set_2cta(int on)
 {
     b200q::fp8::g_use_2cta = on ? 1 : 0;
+    return 0;
+}
+
+int b200q_fp8_set_tma_store(int on)
+{
+    b200q::fp8::g_tma_store = on ? 1 : 0;
     return 0;
 }
 

@@ -12,9 +12,14 @@
 //     accumulator ("tmem full") on both CTAs at once (a signal multicast, not a data load);
 //   * the epilogue warps of both CTAs hand accumulator buffers back by arriving on the leader's
 //     "tmem empty" barrier (the peer through the cluster address of that barrier).
+// bf16 results leave through shared memory: each epilogue warp packs 32 rows x kCW columns into a
+// swizzled staging buffer and one lane issues a TMA store of that box (whole 32/64-byte row pieces
+// per request instead of 16 bytes per thread; the tensor map clips at the matrix edge).
 // With the SwiGLU epilogue the leader's B half is the gate rows and the peer's the up rows, so every
 // CTA again holds gate | up of its 128 token rows side by side.
 #pragma once
+#include <type_traits>
+
 #include "gemm_fp8.cuh"
 
 namespace b200q {
@@ -26,7 +31,8 @@ struct PairCfg {
     static constexpr int kBHalfRows = BN / 2;                           // B rows each CTA loads
     static constexpr int kStageBytes = kBM * kBK + kBHalfRows * kBK;    // A 16 KiB + B half (16 or 14 KiB)
     static constexpr int kStages = 6;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kStoreBytes = 4 * 2 * 2048;                    // per epilogue warp two 32-row x 64-byte staging buffers
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
     static_assert(kStageBytes % 1024 == 0 && BN % 32 == 0, "tile shape");
 };
 
@@ -42,7 +48,7 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
 template <int EPI, typename OutT, int BN>
 __global__ void __launch_bounds__(kBaseThreads, 1)
 gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const __grid_constant__ CUtensorMap tmB2, const Params p)
+                     const __grid_constant__ CUtensorMap tmB2, const __grid_constant__ CUtensorMap tmC, const Params p)
 {
     using PC = PairCfg<BN>;
     constexpr int kStages = PC::kStages;
@@ -50,7 +56,8 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     constexpr int kPairBN = BN;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bar_base = smem_base + kStages * kPairStageBytes;
+    const uint32_t store_base = smem_base + kStages * kPairStageBytes;     // epilogue staging (1024-byte aligned)
+    const uint32_t bar_base = store_base + PC::kStoreBytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
@@ -138,6 +145,13 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         OutT* Cbase = static_cast<OutT*>(p.C);
         const bool ld_ok = ((p.ldc * (long long)sizeof(OutT)) % 16 == 0) && aligned16(p.C);
         const uint32_t leader_tempty0 = ptx::mapa(tempty_bar(0), 0), leader_tempty1 = ptx::mapa(tempty_bar(1), 0);
+        constexpr bool kBf16Out = std::is_same<OutT, __nv_bfloat16>::value;
+        constexpr uint32_t kRowBytes = kCW * 2;                // staging row: 64 or 32 bytes, swizzled over that span
+        constexpr uint32_t kSwzMask = kRowBytes / 16 - 1;
+        const bool tma_store = kBf16Out && p.tma_store != 0;
+        const uint32_t stage_buf = store_base + static_cast<uint32_t>(q) * 4096u;
+        const uint64_t store_policy = ptx::l2_policy_evict_first();
+        uint32_t chunk_no = 0;
         int t = 0; bool ok = true;
         for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
             const int buf = t & 1;
@@ -178,7 +192,29 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                         v[i] = __uint_as_float(r[i]) * s;
                     }
                 }
-                if (row < p.M && col0 < p.N) {
+                if (tma_store) {
+                    if constexpr (kBf16Out) {
+                        const int row0 = row - lane;
+                        if (row0 < p.M && col0 < p.N) {
+                            const uint32_t sbuf = stage_buf + (chunk_no & 1u) * 2048u;
+                            ++chunk_no;
+                            if (lane == 0) ptx::tma_store_wait_read<1>();     // the store that last read this buffer has finished reading
+                            __syncwarp();
+#pragma unroll
+                            for (int j = 0; j < kCW / 8; ++j) {
+                                const uint32_t off = lane * kRowBytes + j * 16u;
+                                const uint32_t phys = off ^ (((off >> 7) & kSwzMask) << 4);
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbuf + phys),
+                                             "r"(pack_bf16x2(v[8 * j + 0], v[8 * j + 1])), "r"(pack_bf16x2(v[8 * j + 2], v[8 * j + 3])),
+                                             "r"(pack_bf16x2(v[8 * j + 4], v[8 * j + 5])), "r"(pack_bf16x2(v[8 * j + 6], v[8 * j + 7]))
+                                             : "memory");
+                            }
+                            ptx::fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) { ptx::tma_store_2d_hint(&tmC, sbuf, col0, row0, store_policy); ptx::tma_store_commit(); }
+                        }
+                    }
+                } else if (row < p.M && col0 < p.N) {
                     const int valid = min(kCW, p.N - col0);
                     OutPack<OutT>::template store<kCW>(Cbase + (long long)row * p.ldc + col0, v, ld_ok && valid == kCW, valid);
                 }
@@ -187,6 +223,7 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(buf ? leader_tempty1 : leader_tempty0);
         }
+        if (lane == 0) ptx::tma_store_wait_all<0>();      // shared memory must outlive the stores that read it
     }
 
     // both CTAs are done with tensor memory (every accumulator was drained) before either frees it

@@ -175,18 +175,23 @@ gemm_nvfp4_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     const uint32_t sa = smem_base + stage * C::kStageBytes;
                     const uint32_t sb = sa + C::kABytes, ssfa = sb + C::kBBytes, ssfb = ssfa + C::kSfaBytes;
                     const uint64_t da = ptx::smem_desc_sw128_kmajor(sa), db = ptx::smem_desc_sw128_kmajor(sb);
-                    for (int ks = 0; ks < ksteps; ++ks) {
+                    // descriptors advance in 16-byte units: one 512-byte scale block = 32
+                    const uint64_t dsfa = ptx::smem_desc_noswizzle_kmajor(ssfa, 16, 128), dsfb = ptx::smem_desc_noswizzle_kmajor(ssfb, 16, 128);
+                    const uint32_t tsfa = tmem_base + C::kSfaCol, tsfb = tmem_base + C::kSfbCol;
+                    auto kstep = [&](int ks) {
                         // scales of this K-step: one 512-byte block for A, kNB blocks for B
-                        ptx::tmem_cp_32x128b_warpx4(tmem_base + C::kSfaCol + 4 * ks,
-                                                    ptx::smem_desc_noswizzle_kmajor(ssfa + ks * kSfBlockBytes, 16, 128));
+                        ptx::tmem_cp_32x128b_warpx4(tsfa + 4 * ks, dsfa + 32u * ks);
 #pragma unroll
                         for (int i = 0; i < C::kNB; ++i)
-                            ptx::tmem_cp_32x128b_warpx4(
-                                tmem_base + C::kSfbCol + 4 * C::kNB * ks + 4 * i,
-                                ptx::smem_desc_noswizzle_kmajor(ssfb + (i * 4 + ks) * kSfBlockBytes, 16, 128));
-                        ptx::umma_mxf4nvf4(d_tmem, da + 2u * ks, db + 2u * ks, idesc,
-                                           tmem_base + C::kSfaCol + 4 * ks,
-                                           tmem_base + C::kSfbCol + 4 * C::kNB * ks + sfb_col_off, (kb | ks) != 0);
+                            ptx::tmem_cp_32x128b_warpx4(tsfb + 4 * C::kNB * ks + 4 * i, dsfb + 32u * (i * 4 + ks));
+                        ptx::umma_mxf4nvf4(d_tmem, da + 2u * ks, db + 2u * ks, idesc, tsfa + 4 * ks,
+                                           tsfb + 4 * C::kNB * ks + sfb_col_off, (kb | ks) != 0);
+                    };
+                    if (ksteps == 4) {             // the single issuing thread is on the critical path: no loop overhead
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) kstep(ks);
+                    } else {
+                        for (int ks = 0; ks < ksteps; ++ks) kstep(ks);
                     }
                     ptx::umma_commit(empty_bar(stage));
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -291,9 +296,16 @@ cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, Params p, cud
 }
 
 int g_tile_n = 256;     // B tile width: 128, 192 or 256 (b200q_nvfp4_set_tile_n)
+int g_use_2cta = 1;     // 1 (default): CTA-pair kernel (gemm_nvfp4_2cta.cu) for tile widths 192 / 256 (b200q_nvfp4_set_2cta)
 
 }  // namespace nvfp4
 }  // namespace b200q
+
+namespace b200q {
+// gemm_nvfp4_2cta.cu: the CTA-pair kernel (256-row tiles, bn = 192 or 256 columns)
+int gemm_nvfp4_blocked_pair(const void* Aq, const void* SFA_blocked, const void* Bq, const void* SFB_blocked, void* C, int M, int N,
+                            int K, float global_a, float global_b, int bn, void* stream);
+}
 
 extern "C" {
 
@@ -323,6 +335,12 @@ int b200q_nvfp4_set_tile_n(int bn)
     return 0;
 }
 
+int b200q_nvfp4_set_2cta(int on)
+{
+    b200q::nvfp4::g_use_2cta = on ? 1 : 0;
+    return 0;
+}
+
 int b200q_gemm_nvfp4_blocked(const void* Aq, const void* SFA_blocked, const void* Bq, const void* SFB_blocked, void* C,
                              int M, int N, int K, float global_a, float global_b, void* stream)
 {
@@ -338,6 +356,8 @@ int b200q_gemm_nvfp4_blocked(const void* Aq, const void* SFA_blocked, const void
     p.status = status_ptr();
     if (p.status == nullptr) return cudaErrorInvalidDevice;
     const int bn = nvfp4::g_tile_n;
+    if (nvfp4::g_use_2cta && bn != 128 && M > 128)
+        return gemm_nvfp4_blocked_pair(Aq, SFA_blocked, Bq, SFB_blocked, C, M, N, K, global_a, global_b, bn, stream);
     CUtensorMap tmA, tmB;
     if (!make_tmap_2d_u8(&tmA, Aq, M, K / 2, K / 2, nvfp4::kBM, nvfp4::kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B))
         return cudaErrorInvalidValue;

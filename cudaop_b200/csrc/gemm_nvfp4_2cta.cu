@@ -1,0 +1,364 @@
+// NVFP4 block-scaled GEMM on CTA pairs (tcgen05 cta_group::2): 256 x BN output tile per pair.
+//
+// Same arithmetic and operand formats as gemm_nvfp4.cu (E2M1 data, one UE4M3 scale per 16 K in the
+// blocked layout, fp32 accumulate, global scales in the epilogue; formats:
+// op/test/arch_primitives/ptx_mma_fp4.cu:49-65,120-144,285-324).  What changes is who loads what:
+// each CTA of a pair loads its own 128 rows of A and their scales, HALF of the B tile (BN/2 rows),
+// and the scales of the WHOLE B tile (its tensor core multiplies its 128 rows by all BN columns,
+// fetching the other half of B from the peer's shared memory).  The B traffic per SM is halved —
+// the one-CTA kernel is limited by the L2 -> shared-memory feed at the FP4 rate.
+// The leader CTA's MMA thread issues, for both CTAs at once, the scale copies into tensor memory
+// (tcgen05.cp.cta_group::2: each CTA copies from its own shared memory into its own TMEM) and the
+// MMAs (tcgen05.mma.cta_group::2 kind::mxf4nvf4, 256 x BN x 64).  Barriers as in gemm_fp8_2cta.cuh:
+// all loads of both CTAs complete on the leader's "full" barrier (.cta_group::2 loads, no
+// multicast), commits with a CTA mask release slots / publish accumulators on both CTAs, the
+// epilogue warps of both CTAs release accumulators on the leader's barrier.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "../../include/b200q.h"
+
+namespace b200q {
+namespace nvfp4p {
+
+constexpr int kBM = 128;                 // rows per CTA (256 per pair)
+constexpr int kBKBytes = 128;            // 256 E2M1 per row and stage
+constexpr int kBKElems = 256;
+constexpr int kThreads = 192;
+constexpr int kSfBlockBytes = 512;
+constexpr uint32_t kTmemCols = 512;
+
+template <int BN>
+struct Cfg {
+    static_assert(BN % 64 == 0 && BN <= 256, "B tile width");
+    static constexpr int kMaxOff = (BN % 128 == 0) ? 0 : 64;
+    static constexpr int kNB = (kMaxOff + BN + 127) / 128;           // scale row-blocks of the whole B tile
+    static constexpr int kABytes = kBM * kBKBytes;
+    static constexpr int kBHalfBytes = (BN / 2) * kBKBytes;
+    static constexpr int kSfaBytes = 4 * kSfBlockBytes;
+    static constexpr int kSfbBytes = kNB * 4 * kSfBlockBytes;
+    static constexpr int kStageBytes = kABytes + kBHalfBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kStoreBytes = 4 * 2 * 4096;                 // per epilogue warp two 32-row x 64-column bf16 staging buffers
+    static constexpr int kStages = (227 * 1024 - 1024 - 256 - kStoreBytes) / kStageBytes > 6 ? 6 : (227 * 1024 - 1024 - 256 - kStoreBytes) / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
+    static constexpr int kAccBufs = (2 * BN + 16 + 16 * kNB <= 512) ? 2 : 1;
+    static constexpr int kSfaCol = kAccBufs * BN;
+    static constexpr int kSfbCol = kSfaCol + 16;
+    static_assert(kStageBytes % 1024 == 0, "stage alignment");
+};
+
+struct Params {
+    int M, N, K;
+    __nv_bfloat16* C;
+    float alpha;
+    int tiles_m, tiles_n;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn)
+{
+    constexpr int kGroup = 8;
+    const int per_group = kGroup * tiles_n;
+    const int g = tile / per_group;
+    const int first = g * kGroup;
+    const int rows = min(kGroup, tiles_m - first);
+    const int r = tile - g * per_group;
+    tm = first + r % rows;
+    tn = r / rows;
+}
+
+// cp.async.bulk.tensor.2d with .cta_group::2 (no multicast): completion barrier may be the peer's
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* tm, uint32_t cluster_bar, int x, int y)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(cluster_bar), "r"(x), "r"(y)
+        : "memory");
+}
+// tcgen05.cp.cta_group::2.32x128b.warpx4: both CTAs of the pair copy 32 rows x 16 bytes from their own
+// shared memory into their own tensor memory
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t smem_desc)
+{
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X
+__device__ __forceinline__ void umma_mxf4nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
+                       const __grid_constant__ CUtensorMap tmC, const Params p)
+{
+    using C = Cfg<BN>;
+    constexpr int kStages = C::kStages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t store_base = smem_base + kStages * C::kStageBytes;      // epilogue staging, 1024-byte aligned
+    const uint32_t bar_base = store_base + C::kStoreBytes;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
+    const uint32_t tmem_slot = bar_base + 8u * (2 * kStages + 4);
+    volatile uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - ptx::smem_u32(smem_raw)));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta_rank = ptx::cluster_ctarank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int num_kb = (p.K + kBKElems - 1) / kBKElems;
+    const int k64_total = p.K / 64;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull_bar(b), 1); ptx::mbar_init(tempty_bar(b), 8); }
+        ptx::fence_mbar_init();
+    }
+    if (warp == 1) { ptx::tmem_alloc_2cta(tmem_slot, kTmemCols); ptx::tmem_relinquish_2cta(); }
+    ptx::tcgen05_fence_before_sync();
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+    ptx::tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer (both CTAs)
+        if (ptx::elect_one()) {
+            ptx::tma_prefetch_desc(&tmA); ptx::tma_prefetch_desc(&tmB);
+            ptx::tma_prefetch_desc(&tmSFA); ptx::tma_prefetch_desc(&tmSFB);
+            int stage = 0; uint32_t phase = 0; bool ok = true;
+            for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
+                int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                const int m0 = tm * (2 * kBM) + static_cast<int>(cta_rank) * kBM;
+                const int n0 = tn * BN;
+                const int rb0 = n0 / 128;
+                const int mb = m0 / 128;                      // scale row-block of this CTA's A rows
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, p.status, 1)) { ok = false; break; }
+                    const uint32_t sa = smem_base + stage * C::kStageBytes;
+                    const uint32_t sb = sa + C::kABytes, ssfa = sb + C::kBHalfBytes, ssfb = ssfa + C::kSfaBytes;
+                    const uint32_t leader_full = ptx::mapa(full_bar(stage), 0);
+                    if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * C::kStageBytes);
+                    tma_load_2d_pair(sa, &tmA, leader_full, kb * kBKBytes, m0);
+                    tma_load_2d_pair(sb, &tmB, leader_full, kb * kBKBytes, n0 + static_cast<int>(cta_rank) * (BN / 2));
+                    // scales: the blocked arrays seen as rows of 256 bytes; one (row-block, K-slab) = 4 blocks = 8 rows
+                    tma_load_2d_pair(ssfa, &tmSFA, leader_full, 0, (mb * k64_total + 4 * kb) * 2);
+#pragma unroll
+                    for (int i = 0; i < C::kNB; ++i)
+                        tma_load_2d_pair(ssfb + i * 4 * kSfBlockBytes, &tmSFB, leader_full, 0, ((rb0 + i) * k64_total + 4 * kb) * 2);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) __nanosleep(200000);
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------- MMA issuer (leader only)
+        if (cta_rank == 0 && ptx::elect_one()) {
+            constexpr uint32_t idesc = ptx::umma_idesc_block_scaled(1, 1, 2 * kBM, BN, 0, 0, 0);
+            int stage = 0; uint32_t phase = 0; bool ok = true;
+            int t = 0;
+            for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
+                const int buf = (C::kAccBufs == 2) ? (t & 1) : 0;
+                const uint32_t par = (C::kAccBufs == 2) ? ((t >> 1) & 1u) : (t & 1u);
+                if (!ptx::mbar_wait(tempty_bar(buf), par ^ 1u, p.status, 2)) { ok = false; break; }
+                ptx::tcgen05_fence_after_sync();
+                int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                const uint32_t sfb_col_off = ((tn * BN) % 128) / 32;
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(full_bar(stage), phase, p.status, 3)) { ok = false; break; }
+                    ptx::tcgen05_fence_after_sync();
+                    const int ksteps = min(4, k64_total - 4 * kb);
+                    const uint32_t sa = smem_base + stage * C::kStageBytes;
+                    const uint32_t sb = sa + C::kABytes, ssfa = sb + C::kBHalfBytes, ssfb = ssfa + C::kSfaBytes;
+                    const uint64_t da = ptx::smem_desc_sw128_kmajor(sa), db = ptx::smem_desc_sw128_kmajor(sb);
+                    const uint64_t dsfa = ptx::smem_desc_noswizzle_kmajor(ssfa, 16, 128), dsfb = ptx::smem_desc_noswizzle_kmajor(ssfb, 16, 128);
+                    const uint32_t tsfa = tmem_base + C::kSfaCol, tsfb = tmem_base + C::kSfbCol;
+                    auto kstep = [&](int ks) {
+                        // descriptors advance in 16-byte units: one 512-byte scale block = 32
+                        tmem_cp_32x128b_warpx4_pair(tsfa + 4 * ks, dsfa + 32u * ks);
+#pragma unroll
+                        for (int i = 0; i < C::kNB; ++i)
+                            tmem_cp_32x128b_warpx4_pair(tsfb + 4 * C::kNB * ks + 4 * i, dsfb + 32u * (i * 4 + ks));
+                        umma_mxf4nvf4_pair(d_tmem, da + 2u * ks, db + 2u * ks, idesc, tsfa + 4 * ks,
+                                           tsfb + 4 * C::kNB * ks + sfb_col_off, (kb | ks) != 0);
+                    };
+                    if (ksteps == 4) {
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) kstep(ks);
+                    } else {
+                        for (int ks = 0; ks < ksteps; ++ks) kstep(ks);
+                    }
+                    ptx::umma_commit_2cta(empty_bar(stage), 3);
+                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::umma_commit_2cta(tfull_bar(buf), 3);
+            }
+            if (!ok) __nanosleep(200000);
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+        // Each warp owns 32 accumulator rows.  64 columns at a time: tensor memory -> registers -> bf16 in a
+        // 128-byte-swizzled staging buffer -> one TMA store of a 32 x 64 box (full 128-byte lines, clipped
+        // at the matrix edge by the tensor map).  Two staging buffers per warp; the accumulator goes back to
+        // the MMA thread as soon as its last column has been read, before the last stores are issued.
+        const int q = warp & 3;
+        const bool tma_ok = ((static_cast<long long>(p.N) * 2) % 16 == 0) && aligned16(p.C);
+        const uint32_t leader_tempty0 = ptx::mapa(tempty_bar(0), 0), leader_tempty1 = ptx::mapa(tempty_bar(1), 0);
+        const uint32_t stage_buf = store_base + static_cast<uint32_t>(q) * 8192u;
+        const uint64_t store_policy = ptx::l2_policy_evict_first();
+        uint32_t chunk_no = 0;
+        int t = 0; bool ok = true;
+        for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
+            const int buf = (C::kAccBufs == 2) ? (t & 1) : 0;
+            const uint32_t par = (C::kAccBufs == 2) ? ((t >> 1) & 1u) : (t & 1u);
+            int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            const int row0 = tm * (2 * kBM) + static_cast<int>(cta_rank) * kBM + q * 32;
+            const int row = row0 + lane;
+            const int n0 = tn * BN;
+            if (!ptx::mbar_wait(tfull_bar(buf), par, p.status, 4)) { ok = false; break; }
+            ptx::tcgen05_fence_after_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 64; ++c) {
+                uint32_t r0[32], r1[32];
+                ptx::tmem_ld_32x32b_x32(taddr + c * 64, r0);
+                ptx::tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
+                ptx::tmem_ld_wait();
+                if (c == BN / 64 - 1) {          // last columns read: the accumulator is free
+                    ptx::tcgen05_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive_cluster(buf ? leader_tempty1 : leader_tempty0);
+                }
+                const int col0 = n0 + c * 64;
+                if (row0 >= p.M || col0 >= p.N) continue;
+                uint4 o[8];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    o[i].x = pack_bf16x2(__uint_as_float(r0[8 * i + 0]) * p.alpha, __uint_as_float(r0[8 * i + 1]) * p.alpha);
+                    o[i].y = pack_bf16x2(__uint_as_float(r0[8 * i + 2]) * p.alpha, __uint_as_float(r0[8 * i + 3]) * p.alpha);
+                    o[i].z = pack_bf16x2(__uint_as_float(r0[8 * i + 4]) * p.alpha, __uint_as_float(r0[8 * i + 5]) * p.alpha);
+                    o[i].w = pack_bf16x2(__uint_as_float(r0[8 * i + 6]) * p.alpha, __uint_as_float(r0[8 * i + 7]) * p.alpha);
+                    o[4 + i].x = pack_bf16x2(__uint_as_float(r1[8 * i + 0]) * p.alpha, __uint_as_float(r1[8 * i + 1]) * p.alpha);
+                    o[4 + i].y = pack_bf16x2(__uint_as_float(r1[8 * i + 2]) * p.alpha, __uint_as_float(r1[8 * i + 3]) * p.alpha);
+                    o[4 + i].z = pack_bf16x2(__uint_as_float(r1[8 * i + 4]) * p.alpha, __uint_as_float(r1[8 * i + 5]) * p.alpha);
+                    o[4 + i].w = pack_bf16x2(__uint_as_float(r1[8 * i + 6]) * p.alpha, __uint_as_float(r1[8 * i + 7]) * p.alpha);
+                }
+                if (tma_ok) {
+                    const uint32_t sbuf = stage_buf + (chunk_no & 1u) * 4096u;
+                    ++chunk_no;
+                    if (lane == 0) ptx::tma_store_wait_read<1>();      // the store that last read this buffer is done with it
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)                        // 16-byte unit j of row `lane`, 128-byte swizzle
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbuf + lane * 128u + ((j ^ (lane & 7)) << 4)),
+                                     "r"(o[j].x), "r"(o[j].y), "r"(o[j].z), "r"(o[j].w) : "memory");
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) { ptx::tma_store_2d_hint(&tmC, sbuf, col0, row0, store_policy); ptx::tma_store_commit(); }
+                } else if (row < p.M) {
+                    __nv_bfloat16* dst = p.C + static_cast<size_t>(row) * p.N + col0;
+                    const int valid = min(64, p.N - col0);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t w[4] = {o[j].x, o[j].y, o[j].z, o[j].w};
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            if (8 * j + e < valid)
+                                reinterpret_cast<uint16_t*>(dst)[8 * j + e] =
+                                    static_cast<uint16_t>((e & 1) ? (w[e >> 1] >> 16) : (w[e >> 1] & 0xFFFFu));
+                    }
+                }
+            }
+        }
+        if (lane == 0) ptx::tma_store_wait_all<0>();       // shared memory must outlive the stores that read it
+    }
+
+    ptx::tcgen05_fence_before_sync();
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+    if (warp == 1) {
+        ptx::tcgen05_fence_after_sync();
+        ptx::tmem_dealloc_2cta(tmem_base, kTmemCols);
+    }
+}
+
+template <int BN>
+cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA, const CUtensorMap& tmSFB,
+                   const CUtensorMap& tmC, Params p, cudaStream_t stream)
+{
+    auto kernel = gemm_nvfp4_2cta_kernel<BN>;
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 64 && !configured[dev]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    p.tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM);
+    p.tiles_n = (p.N + BN - 1) / BN;
+    const int sms = num_sms();
+    if (sms <= 0) return cudaErrorInvalidDevice;
+    const int tiles = p.tiles_m * p.tiles_n;
+    const int pairs = tiles < sms / 2 ? tiles : sms / 2;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = Cfg<BN>::kSmemBytes; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, tmA, tmB, tmSFA, tmSFB, tmC, p);
+}
+
+}  // namespace nvfp4p
+}  // namespace b200q
+
+// Called by b200q_gemm_nvfp4_blocked when the CTA-pair kernel is selected (b200q_nvfp4_set_2cta).
+namespace b200q {
+int gemm_nvfp4_blocked_pair(const void* Aq, const void* SFA_blocked, const void* Bq, const void* SFB_blocked,
+                                             void* C, int M, int N, int K, float global_a, float global_b, int bn, void* stream)
+{
+    if (Aq == nullptr || SFA_blocked == nullptr || Bq == nullptr || SFB_blocked == nullptr || C == nullptr)
+        return cudaErrorInvalidValue;
+    if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0) return cudaErrorInvalidValue;
+    if (!aligned16(Aq) || !aligned16(Bq) || !aligned16(SFA_blocked) || !aligned16(SFB_blocked)) return cudaErrorInvalidValue;
+    if (bn != 192 && bn != 256) return cudaErrorInvalidValue;
+    nvfp4p::Params p{};
+    p.M = M; p.N = N; p.K = K; p.C = static_cast<__nv_bfloat16*>(C); p.alpha = global_a * global_b;
+    p.status = status_ptr();
+    if (p.status == nullptr) return cudaErrorInvalidDevice;
+    CUtensorMap tmA, tmB, tmSFA, tmSFB;
+    if (!make_tmap_2d_u8(&tmA, Aq, M, K / 2, K / 2, nvfp4p::kBM, nvfp4p::kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
+    if (!make_tmap_2d_u8(&tmB, Bq, N, K / 2, K / 2, bn / 2, nvfp4p::kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
+    const uint64_t rows_a = static_cast<uint64_t>((M + 127) / 128) * (K / 64) * 2, rows_b = static_cast<uint64_t>((N + 127) / 128) * (K / 64) * 2;
+    if (!make_tmap_2d_u8(&tmSFA, SFA_blocked, rows_a, 256, 256, 8, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return cudaErrorInvalidValue;
+    if (!make_tmap_2d_u8(&tmSFB, SFB_blocked, rows_b, 256, 256, 8, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return cudaErrorInvalidValue;
+    // C as a bf16 matrix with 32-row x 64-column boxes for the epilogue's stores; when N or the pointer rules
+    // out a tensor map (row pitch not a multiple of 16 bytes) the kernel stores element-wise and the map is
+    // a never-used placeholder over A.
+    CUtensorMap tmC = tmA;
+    if ((static_cast<long long>(N) * 2) % 16 == 0 && aligned16(C)) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(N) * 2};
+        const uint32_t box[2] = {64, 32};
+        if (encode_tiled(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (bn == 192) return nvfp4p::launch<192>(tmA, tmB, tmSFA, tmSFB, tmC, p, s);
+    return nvfp4p::launch<256>(tmA, tmB, tmSFA, tmSFB, tmC, p, s);
+}
+}  // namespace b200q

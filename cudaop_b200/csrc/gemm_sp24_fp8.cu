@@ -135,9 +135,16 @@ gemm_sp24_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 #pragma unroll
                     for (int h = 0; h < 2; ++h)      // metadata of logical K [128h, 128h+128): 4 columns
                         ptx::tmem_cp_128x128b(e_tmem + 4 * h, ptx::smem_desc_noswizzle_kmajor(se + h * kBM * 16, 16, 128));
-                    for (int ks = 0; ks < steps; ++ks) {
-                        const uint64_t db = ptx::smem_desc_sw128_kmajor(sb + (ks >> 1) * C::kBHalf) + 4u * (ks & 1);
-                        ptx::umma_sp_f8f6f4(d_tmem, da + 2u * ks, db, idesc, e_tmem + 2 * ks, (kb | ks) != 0);
+                    const uint64_t db0 = ptx::smem_desc_sw128_kmajor(sb), db1 = ptx::smem_desc_sw128_kmajor(sb + C::kBHalf);
+                    auto kstep = [&](int ks) {
+                        ptx::umma_sp_f8f6f4(d_tmem, da + 2u * ks, ((ks >> 1) ? db1 : db0) + 4u * (ks & 1), idesc, e_tmem + 2 * ks,
+                                            (kb | ks) != 0);
+                    };
+                    if (steps == 4) {                // the single issuing thread is on the critical path: no loop overhead
+#pragma unroll
+                        for (int ks = 0; ks < 4; ++ks) kstep(ks);
+                    } else {
+                        for (int ks = 0; ks < steps; ++ks) kstep(ks);
                     }
                     ptx::umma_commit(empty_bar(stage));
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }

@@ -156,6 +156,28 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tm, uint32_t sme
         ::"l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_src), "r"(x), "r"(y)
         : "memory");
 }
+// createpolicy: an L2 eviction-priority descriptor for the cache-hinted forms below
+__device__ __forceinline__ uint64_t l2_policy_evict_first()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last()
+{
+    uint64_t pol;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+    return pol;
+}
+// TMA store with an L2 cache hint (results that nobody re-reads soon: evict first, so they do not push
+// the operands out of L2)
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap* tm, uint32_t smem_src, int x, int y, uint64_t policy)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+        ::"l"(reinterpret_cast<uint64_t>(tm)), "r"(smem_src), "r"(x), "r"(y), "l"(policy)
+        : "memory");
+}
 __device__ __forceinline__ void tma_store_commit()
 {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");

@@ -21,8 +21,11 @@ def main() -> None:
     ap.add_argument("--size", type=int, default=8192)
     ap.add_argument("--m", type=int, default=16)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--nvfp4-pair", type=int, default=-1, help="1/0: force the CTA-pair / one-CTA NVFP4 kernel")
     a = ap.parse_args()
     L = ops.lib()
+    if a.nvfp4_pair >= 0:
+        L.b200q_nvfp4_set_2cta(a.nvfp4_pair)
     st = torch.cuda.current_stream().cuda_stream
     S = a.size
     u8 = lambda *shape, hi=120: torch.randint(0, hi, shape, dtype=torch.uint8, device="cuda")

@@ -105,8 +105,11 @@ int b200q_fp8_set_tile_n(int bn);      /* 0 = chosen per problem (default), 224 
 int b200q_fp8_set_sm_limit(int sms);
 int b200q_allreduce_set_reserved_smem(int bytes);
 int b200q_fp8_set_2cta(int on);        /* FP8 GEMMs on CTA pairs (tcgen05 cta_group::2, 256-row tiles); default on */
+int b200q_fp8_set_tma_store(int on);   /* CTA-pair FP8 kernels: bf16 results via shared memory + TMA stores (default on) */
 int b200q_fp8_set_reducer_stride(int stride);   /* fused all-reduce: every stride-th CTA reduces, 1..16 */
 int b200q_nvfp4_set_tile_n(int bn);
+int b200q_nvfp4_set_2cta(int on);      /* NVFP4 GEMM on CTA pairs (256 x 192 / 256 x 256 tiles per pair) when M > 128 and the
+                                        * tile width is not 128; default on */
 int b200q_w4a16_set_impl(int impl);     /* 0 = warp-MMA kernel (default, measured faster), 1 = tcgen05 kernel */
 int b200q_w4a16_set_pdl(int on);        /* programmatic dependent launch of the tcgen05 W4A16 kernel (default off) */
 int b200q_sp24_set_tile_n(int bn);

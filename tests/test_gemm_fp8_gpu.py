@@ -11,13 +11,17 @@ from tests.util import CORES, assert_bar, bf16_to_f32, dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[1, 0], ids=["cta_pair", "one_cta"], autouse=True)
+@pytest.fixture(params=[(1, 1), (1, 0), (0, 0)], ids=["cta_pair", "cta_pair_direct_stores", "one_cta"], autouse=True)
 def kernel_variant(request):
-    """Both FP8 kernels: CTA pairs (tcgen05 cta_group::2, default) and the one-CTA kernel."""
+    """The FP8 kernels: CTA pairs (tcgen05 cta_group::2, default; results through TMA stores or stored
+    straight from registers) and the one-CTA kernel."""
     import cudaop_b200 as ops
-    ops.lib().b200q_fp8_set_2cta(request.param)
+    pair, tma_store = request.param
+    ops.lib().b200q_fp8_set_2cta(pair)
+    ops.lib().b200q_fp8_set_tma_store(tma_store)
     yield request.param
     ops.lib().b200q_fp8_set_2cta(1)
+    ops.lib().b200q_fp8_set_tma_store(1)
 
 
 def _run(aq, bq, sa, sb):

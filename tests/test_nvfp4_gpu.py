@@ -9,12 +9,17 @@ from tests.util import CORES, assert_bar, bf16_to_f32, dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[128, 192, 256])
+@pytest.fixture(params=[(128, 0), (192, 0), (256, 0), (192, 1), (256, 1)],
+                ids=["one_cta_128", "one_cta_192", "one_cta_256", "cta_pair_192", "cta_pair_256"])
 def tile_n(request):
+    """Every kernel variant: one-CTA tiles of 128/192/256 columns and CTA-pair tiles (256 rows) of 192/256."""
     import cudaop_b200 as ops
-    ops.lib().b200q_nvfp4_set_tile_n(request.param)
-    yield request.param
+    bn, pair = request.param
+    ops.lib().b200q_nvfp4_set_tile_n(bn)
+    ops.lib().b200q_nvfp4_set_2cta(pair)
+    yield bn
     ops.lib().b200q_nvfp4_set_tile_n(256)
+    ops.lib().b200q_nvfp4_set_2cta(1)
 
 
 def _ref(aq, sfa, ga, bq, sfb, gb):
@@ -51,7 +56,8 @@ def test_every_nibble_and_power_of_two_scales_exact(tile_n):
     assert np.array_equal(bf16_to_f32(out), oracle.decode_bf16(oracle.encode_bf16(ref.astype(np.float32))))
 
 
-@pytest.mark.parametrize("shape", [(1, 8, 64), (128, 128, 64), (130, 200, 320), (300, 520, 832), (512, 1024, 2048)])
+@pytest.mark.parametrize("shape", [(1, 8, 64), (128, 128, 64), (130, 200, 320), (260, 100, 128), (300, 520, 832),
+                                   (512, 1024, 2048), (777, 1000, 1088)])
 def test_quantised_normal_operands(tile_n, shape):
     import cudaop_b200 as ops
     M, N, K = shape
