@@ -1,5 +1,6 @@
-// INT4 weight-only GEMM for decode shapes on warp-level mma.sync (kept as the alternative
-// implementation behind b200q_w4a16_set_impl(0); the default is the tcgen05 kernel in gemm_w4a16_tc.cu):
+// INT4 weight-only GEMM for decode shapes on warp-level mma.sync (the default of b200q_gemm_w4a16 for
+// two tokens and more; one token goes to the CUDA-core kernel in gemm_w4a16_gemv.cu, and the tcgen05
+// kernel in gemm_w4a16_tc.cu is selectable with b200q_w4a16_set_impl(1)):
 //   Y[M,N] (bf16) = X[M,K] (bf16) * dequant(Wq)[N,K]^T,  w[n,k] = q[n,k] * S[n, k/128]
 // Wq packs two signed 4-bit weights per byte along K, low nibble = lower K index
 // (op/test/arch_primitives/ptx_mma_integer.cu:93-108); S is fp16, one scale per 128 K, no zero point.

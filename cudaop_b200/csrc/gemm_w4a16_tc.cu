@@ -336,18 +336,23 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
     }
 }
 
-int g_impl = 0;      // 0 = the warp-MMA kernel in gemm_w4a16.cu (default: measured faster), 1 = tcgen05 kernel (this file)
-int g_pdl = 0;       // programmatic dependent launch (b200q_w4a16_set_pdl); measured slower, off by default
+int g_impl = 0;      // 0 = by M: CUDA-core GEMV (gemm_w4a16_gemv.cu) for one token, else the warp-MMA kernel (gemm_w4a16.cu);
+                     // 1 = tcgen05 kernel (this file); 2 = warp-MMA kernel for every M; 3 = GEMV up to 4 tokens
+int g_pdl = 0;       // programmatic dependent launch (b200q_w4a16_set_pdl) of the GEMV and tcgen05 kernels, off by default
 
 }  // namespace w4tc
 }  // namespace b200q
 
 extern "C" int b200q_gemm_w4a16_warp_mma(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K,
                                          int group, void* stream);
+namespace b200q {
+// gemm_w4a16_gemv.cu: CUDA-core kernel for M <= 4
+int gemm_w4a16_gemv(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, int pdl, void* stream);
+}
 
 extern "C" int b200q_w4a16_set_impl(int impl)
 {
-    if (impl != 0 && impl != 1) return cudaErrorInvalidValue;
+    if (impl < 0 || impl > 3) return cudaErrorInvalidValue;
     b200q::w4tc::g_impl = impl;
     return 0;
 }
@@ -362,7 +367,10 @@ extern "C" int b200q_gemm_w4a16(const void* X, const void* Wq, const void* S, vo
                                 void* stream)
 {
     using namespace b200q;
-    if (w4tc::g_impl == 0) return b200q_gemm_w4a16_warp_mma(X, Wq, S, Y, M, N, K, group, stream);
+    if (M == 1 && w4tc::g_impl == 0)      // measured: faster than the warp-MMA kernel for one token only
+        return gemm_w4a16_gemv(X, Wq, S, Y, M, N, K, group, w4tc::g_pdl, stream);
+    if (M <= 4 && w4tc::g_impl == 3) return gemm_w4a16_gemv(X, Wq, S, Y, M, N, K, group, w4tc::g_pdl, stream);
+    if (w4tc::g_impl != 1) return b200q_gemm_w4a16_warp_mma(X, Wq, S, Y, M, N, K, group, stream);
     if (X == nullptr || Wq == nullptr || S == nullptr || Y == nullptr) return cudaErrorInvalidValue;
     if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;
     if (group != w4tc::kGroup || K % w4tc::kGroup != 0) return cudaErrorInvalidValue;

@@ -9,20 +9,24 @@ from tests.util import CORES, assert_bar, bf16_to_f32, dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[1, 0], ids=["tcgen05", "warp_mma"], autouse=True)
+@pytest.fixture(params=[(0, 0), (3, 1), (1, 0), (2, 0)], ids=["by_m", "gemv_pdl", "tcgen05", "warp_mma"], autouse=True)
 def impl(request):
-    """Both implementations behind b200q_gemm_w4a16: the tcgen05 kernel (default) and the warp-MMA one."""
+    """Every implementation behind b200q_gemm_w4a16: the default (CUDA-core GEMV for one token, warp-MMA
+    kernel above), the GEMV for up to four tokens with programmatic dependent launch, the tcgen05 kernel,
+    the warp-MMA kernel for every M."""
     import cudaop_b200 as ops
-    ops.lib().b200q_w4a16_set_impl(request.param)
+    ops.lib().b200q_w4a16_set_impl(request.param[0])
+    ops.lib().b200q_w4a16_set_pdl(request.param[1])
     yield request.param
     ops.lib().b200q_w4a16_set_impl(0)
+    ops.lib().b200q_w4a16_set_pdl(0)
 
 
 def _w4_ref(xb, wq, s, group=128):
     return oracle.gemm_f32(oracle.decode_bf16(xb), oracle.dequant_w4(wq, s, group), threads=CORES)
 
 
-@pytest.mark.parametrize("M", [1, 16])
+@pytest.mark.parametrize("M", [1, 2, 4, 16])
 def test_config_decode_4096(M):
     # M in {1,16}, N=K=4096, ints in [-8,7], group 128 fp16 scales U(0.005,0.02), bf16 N(0,1) activations
     import cudaop_b200 as ops
@@ -49,7 +53,7 @@ def test_int4_known_answer_is_exact():
 
 
 @pytest.mark.parametrize("shape", [(1, 32, 128), (3, 33, 256), (16, 100, 1024), (17, 64, 384), (40, 4096, 2048),
-                                   (2, 11008, 4096)])
+                                   (2, 11008, 4096), (1, 4096, 11008), (4, 130, 9344), (3, 7, 1152)])
 def test_ragged_shapes(shape):
     import cudaop_b200 as ops
     M, N, K = shape
