@@ -337,7 +337,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
 }
 
 int g_impl = 0;      // 0 = by M: CUDA-core GEMV (gemm_w4a16_gemv.cu) for one token, else the warp-MMA kernel (gemm_w4a16.cu);
-                     // 1 = tcgen05 kernel (this file); 2 = warp-MMA kernel for every M; 3 = GEMV up to 4 tokens
+                     // 1 = tcgen05 kernel (this file); 2 = warp-MMA kernel for every M; 3 / 4 = GEMV up to 4 tokens, weights
+                     // through shared memory (dp4a arithmetic) / in registers (fp32 arithmetic)
 int g_pdl = 0;       // programmatic dependent launch (b200q_w4a16_set_pdl) of the GEMV and tcgen05 kernels, off by default
 
 }  // namespace w4tc
@@ -347,12 +348,13 @@ extern "C" int b200q_gemm_w4a16_warp_mma(const void* X, const void* Wq, const vo
                                          int group, void* stream);
 namespace b200q {
 // gemm_w4a16_gemv.cu: CUDA-core kernel for M <= 4
-int gemm_w4a16_gemv(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, int pdl, void* stream);
+int gemm_w4a16_gemv(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, int pdl, int form,
+                    void* stream);
 }
 
 extern "C" int b200q_w4a16_set_impl(int impl)
 {
-    if (impl < 0 || impl > 3) return cudaErrorInvalidValue;
+    if (impl < 0 || impl > 4) return cudaErrorInvalidValue;
     b200q::w4tc::g_impl = impl;
     return 0;
 }
@@ -367,9 +369,15 @@ extern "C" int b200q_gemm_w4a16(const void* X, const void* Wq, const void* S, vo
                                 void* stream)
 {
     using namespace b200q;
-    if (M == 1 && w4tc::g_impl == 0)      // measured: faster than the warp-MMA kernel for one token only
-        return gemm_w4a16_gemv(X, Wq, S, Y, M, N, K, group, w4tc::g_pdl, stream);
-    if (M <= 4 && w4tc::g_impl == 3) return gemm_w4a16_gemv(X, Wq, S, Y, M, N, K, group, w4tc::g_pdl, stream);
+    if (M == 1 && w4tc::g_impl == 0) {
+        // one token: CUDA cores.  Measured (K = 4096, 80 weight sets cycled in a graph): up to 8 MiB of weights the
+        // form with the weights in registers is ahead (4096 rows: 4.7 vs 5.1 us), beyond it the shared-memory /
+        // dp4a form (8192 rows: 6.6 vs 8.4 us).
+        const bool big = static_cast<long long>(N) * (K / 2) > (8ll << 20);
+        return gemm_w4a16_gemv(X, Wq, S, Y, M, N, K, group, w4tc::g_pdl, big ? 0 : 1, stream);
+    }
+    if (M <= 4 && (w4tc::g_impl == 3 || w4tc::g_impl == 4))
+        return gemm_w4a16_gemv(X, Wq, S, Y, M, N, K, group, w4tc::g_pdl, w4tc::g_impl == 4 ? 1 : 0, stream);
     if (w4tc::g_impl != 1) return b200q_gemm_w4a16_warp_mma(X, Wq, S, Y, M, N, K, group, stream);
     if (X == nullptr || Wq == nullptr || S == nullptr || Y == nullptr) return cudaErrorInvalidValue;
     if (M <= 0 || N <= 0 || K <= 0) return cudaErrorInvalidValue;

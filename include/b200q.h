@@ -111,7 +111,8 @@ int b200q_nvfp4_set_tile_n(int bn);
 int b200q_nvfp4_set_2cta(int on);      /* NVFP4 GEMM on CTA pairs (256 x 192 / 256 x 256 tiles per pair) when M > 128 and the
                                         * tile width is not 128; default on */
 int b200q_w4a16_set_impl(int impl);     /* 0 = by M (default): CUDA-core GEMV for one token, warp-MMA kernel above;
-                                         * 1 = tcgen05 kernel; 2 = warp-MMA kernel for every M; 3 = GEMV up to 4 tokens */
+                                         * 1 = tcgen05 kernel; 2 = warp-MMA kernel for every M; 3 / 4 = the two GEMV forms
+                                         * (shared memory + dp4a / registers + fp32) for up to 4 tokens */
 int b200q_w4a16_set_pdl(int on);        /* programmatic dependent launch of the GEMV / tcgen05 W4A16 kernels (default off):
                                          * the call may start streaming its weights while the previous kernel of the stream
                                          * still runs, so that kernel must not be the one that writes Wq or S */

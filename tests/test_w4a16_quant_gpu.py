@@ -9,11 +9,12 @@ from tests.util import CORES, assert_bar, bf16_to_f32, dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[(0, 0), (3, 1), (1, 0), (2, 0)], ids=["by_m", "gemv_pdl", "tcgen05", "warp_mma"], autouse=True)
+@pytest.fixture(params=[(0, 0), (3, 1), (4, 0), (1, 0), (2, 0)], ids=["by_m", "gemv_pdl", "gemv_regs", "tcgen05", "warp_mma"],
+                autouse=True)
 def impl(request):
     """Every implementation behind b200q_gemm_w4a16: the default (CUDA-core GEMV for one token, warp-MMA
-    kernel above), the GEMV for up to four tokens with programmatic dependent launch, the tcgen05 kernel,
-    the warp-MMA kernel for every M."""
+    kernel above), the GEMV for up to four tokens with programmatic dependent launch, its form with the
+    weights in registers, the tcgen05 kernel, the warp-MMA kernel for every M."""
     import cudaop_b200 as ops
     ops.lib().b200q_w4a16_set_impl(request.param[0])
     ops.lib().b200q_w4a16_set_pdl(request.param[1])
