@@ -12,7 +12,7 @@
 // MMAs (tcgen05.mma.cta_group::2 kind::mxf4nvf4, 256 x BN x 64).  Barriers as in gemm_fp8_2cta.cuh:
 // all loads of both CTAs complete on the leader's "full" barrier (.cta_group::2 loads, no
 // multicast), commits with a CTA mask release slots / publish accumulators on both CTAs, the
-// epilogue warps of both CTAs release accumulators on the leader's barrier.
+// epilogue warps of both CTAs (eight per CTA, two per TMEM lane quadrant) release accumulators on the leader's barrier.
 #include "common.cuh"
 #include "ptx.cuh"
 #include "../../include/b200q.h"
@@ -23,7 +23,7 @@ namespace nvfp4p {
 constexpr int kBM = 128;                 // rows per CTA (256 per pair)
 constexpr int kBKBytes = 128;            // 256 E2M1 per row and stage
 constexpr int kBKElems = 256;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;            // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quadrant)
 constexpr int kSfBlockBytes = 512;
 constexpr uint32_t kTmemCols = 512;
 
@@ -37,7 +37,7 @@ struct Cfg {
     static constexpr int kSfaBytes = 4 * kSfBlockBytes;
     static constexpr int kSfbBytes = kNB * 4 * kSfBlockBytes;
     static constexpr int kStageBytes = kABytes + kBHalfBytes + kSfaBytes + kSfbBytes;
-    static constexpr int kStoreBytes = 4 * 2 * 4096;                 // per epilogue warp two 32-row x 64-column bf16 staging buffers
+    static constexpr int kStoreBytes = 8 * 4096;                     // per epilogue warp one 32-row x 64-column bf16 staging buffer
     static constexpr int kStages = (227 * 1024 - 1024 - 256 - kStoreBytes) / kStageBytes > 6 ? 6 : (227 * 1024 - 1024 - 256 - kStoreBytes) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
     static constexpr int kAccBufs = (2 * BN + 16 + 16 * kNB <= 512) ? 2 : 1;
@@ -121,7 +121,7 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull_bar(b), 1); ptx::mbar_init(tempty_bar(b), 8); }
+        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull_bar(b), 1); ptx::mbar_init(tempty_bar(b), 16); }
         ptx::fence_mbar_init();
     }
     if (warp == 1) { ptx::tmem_alloc_2cta(tmem_slot, kTmemCols); ptx::tmem_relinquish_2cta(); }
@@ -208,16 +208,18 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         }
     } else {
         // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
-        // Each warp owns 32 accumulator rows.  64 columns at a time: tensor memory -> registers -> bf16 in a
-        // 128-byte-swizzled staging buffer -> one TMA store of a 32 x 64 box (full 128-byte lines, clipped
-        // at the matrix edge by the tensor map).  Two staging buffers per warp; the accumulator goes back to
-        // the MMA thread as soon as its last column has been read, before the last stores are issued.
+        // Two warps per TMEM lane quadrant: each owns 32 accumulator rows and up to 128 of the tile's columns.
+        // It reads all its columns into registers in one go and hands the accumulator back to the MMA thread
+        // (with a single accumulator the tensor pipe idles for exactly this long), then, 64 columns at a
+        // time: bf16 into a 128-byte-swizzled staging buffer -> one TMA store of a 32 x 64 box (full 128-byte
+        // lines, clipped at the matrix edge by the tensor map).
         const int q = warp & 3;
+        const int col_begin = ((warp - 2) >> 2) * 128;                       // first tile column of this warp
+        const int nchunks = (min(BN, col_begin + 128) - col_begin) / 64;     // 2, or 1 for the last 64 of a 192-wide tile
         const bool tma_ok = ((static_cast<long long>(p.N) * 2) % 16 == 0) && aligned16(p.C);
         const uint32_t leader_tempty0 = ptx::mapa(tempty_bar(0), 0), leader_tempty1 = ptx::mapa(tempty_bar(1), 0);
-        const uint32_t stage_buf = store_base + static_cast<uint32_t>(q) * 8192u;
+        const uint32_t sbuf = store_base + static_cast<uint32_t>(warp - 2) * 4096u;
         const uint64_t store_policy = ptx::l2_policy_evict_first();
-        uint32_t chunk_no = 0;
         int t = 0; bool ok = true;
         for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
             const int buf = (C::kAccBufs == 2) ? (t & 1) : 0;
@@ -225,39 +227,38 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
             const int row0 = tm * (2 * kBM) + static_cast<int>(cta_rank) * kBM + q * 32;
             const int row = row0 + lane;
-            const int n0 = tn * BN;
+            const int n0 = tn * BN + col_begin;
             if (!ptx::mbar_wait(tfull_bar(buf), par, p.status, 4)) { ok = false; break; }
             ptx::tcgen05_fence_after_sync();
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-#pragma unroll 1
-            for (int c = 0; c < BN / 64; ++c) {
-                uint32_t r0[32], r1[32];
-                ptx::tmem_ld_32x32b_x32(taddr + c * 64, r0);
-                ptx::tmem_ld_32x32b_x32(taddr + c * 64 + 32, r1);
-                ptx::tmem_ld_wait();
-                if (c == BN / 64 - 1) {          // last columns read: the accumulator is free
-                    ptx::tcgen05_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive_cluster(buf ? leader_tempty1 : leader_tempty0);
-                }
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN + col_begin;
+            uint32_t r[4][32];
+            ptx::tmem_ld_32x32b_x32(taddr, r[0]);
+            ptx::tmem_ld_32x32b_x32(taddr + 32, r[1]);
+            if (nchunks == 2) {
+                ptx::tmem_ld_32x32b_x32(taddr + 64, r[2]);
+                ptx::tmem_ld_32x32b_x32(taddr + 96, r[3]);
+            }
+            ptx::tmem_ld_wait();
+            ptx::tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(buf ? leader_tempty1 : leader_tempty0);     // the accumulator is free
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
                 const int col0 = n0 + c * 64;
-                if (row0 >= p.M || col0 >= p.N) continue;
+                if (c >= nchunks || row0 >= p.M || col0 >= p.N) continue;
                 uint4 o[8];
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    o[i].x = pack_bf16x2(__uint_as_float(r0[8 * i + 0]) * p.alpha, __uint_as_float(r0[8 * i + 1]) * p.alpha);
-                    o[i].y = pack_bf16x2(__uint_as_float(r0[8 * i + 2]) * p.alpha, __uint_as_float(r0[8 * i + 3]) * p.alpha);
-                    o[i].z = pack_bf16x2(__uint_as_float(r0[8 * i + 4]) * p.alpha, __uint_as_float(r0[8 * i + 5]) * p.alpha);
-                    o[i].w = pack_bf16x2(__uint_as_float(r0[8 * i + 6]) * p.alpha, __uint_as_float(r0[8 * i + 7]) * p.alpha);
-                    o[4 + i].x = pack_bf16x2(__uint_as_float(r1[8 * i + 0]) * p.alpha, __uint_as_float(r1[8 * i + 1]) * p.alpha);
-                    o[4 + i].y = pack_bf16x2(__uint_as_float(r1[8 * i + 2]) * p.alpha, __uint_as_float(r1[8 * i + 3]) * p.alpha);
-                    o[4 + i].z = pack_bf16x2(__uint_as_float(r1[8 * i + 4]) * p.alpha, __uint_as_float(r1[8 * i + 5]) * p.alpha);
-                    o[4 + i].w = pack_bf16x2(__uint_as_float(r1[8 * i + 6]) * p.alpha, __uint_as_float(r1[8 * i + 7]) * p.alpha);
-                }
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t (&v)[32] = r[2 * c + h];
+                        o[4 * h + i].x = pack_bf16x2(__uint_as_float(v[8 * i + 0]) * p.alpha, __uint_as_float(v[8 * i + 1]) * p.alpha);
+                        o[4 * h + i].y = pack_bf16x2(__uint_as_float(v[8 * i + 2]) * p.alpha, __uint_as_float(v[8 * i + 3]) * p.alpha);
+                        o[4 * h + i].z = pack_bf16x2(__uint_as_float(v[8 * i + 4]) * p.alpha, __uint_as_float(v[8 * i + 5]) * p.alpha);
+                        o[4 * h + i].w = pack_bf16x2(__uint_as_float(v[8 * i + 6]) * p.alpha, __uint_as_float(v[8 * i + 7]) * p.alpha);
+                    }
                 if (tma_ok) {
-                    const uint32_t sbuf = stage_buf + (chunk_no & 1u) * 4096u;
-                    ++chunk_no;
-                    if (lane == 0) ptx::tma_store_wait_read<1>();      // the store that last read this buffer is done with it
+                    if (lane == 0) ptx::tma_store_wait_read<0>();      // the store that last read the buffer is done with it
                     __syncwarp();
 #pragma unroll
                     for (int j = 0; j < 8; ++j)                        // 16-byte unit j of row `lane`, 128-byte swizzle
