@@ -74,6 +74,13 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtens
         ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(cluster_bar), "r"(x), "r"(y)
         : "memory");
 }
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap* tm, uint32_t cluster_bar, int x, int y, int z)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
 // tcgen05.cp.cta_group::2.32x128b.warpx4: both CTAs of the pair copy 32 rows x 16 bytes from their own
 // shared memory into their own tensor memory
 __device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t smem_desc)
@@ -151,11 +158,10 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * C::kStageBytes);
                     tma_load_2d_pair(sa, &tmA, leader_full, kb * kBKBytes, m0);
                     tma_load_2d_pair(sb, &tmB, leader_full, kb * kBKBytes, n0 + static_cast<int>(cta_rank) * (BN / 2));
-                    // scales: the blocked arrays seen as rows of 256 bytes; one (row-block, K-slab) = 4 blocks = 8 rows
-                    tma_load_2d_pair(ssfa, &tmSFA, leader_full, 0, (mb * k64_total + 4 * kb) * 2);
-#pragma unroll
-                    for (int i = 0; i < C::kNB; ++i)
-                        tma_load_2d_pair(ssfb + i * 4 * kSfBlockBytes, &tmSFB, leader_full, 0, ((rb0 + i) * k64_total + 4 * kb) * 2);
+                    // scales: the blocked arrays as [row block][K/64 * 2 rows of 256 bytes]; a K slab is 8 such rows,
+                    // and one box takes them for all row blocks of the B tile at once
+                    tma_load_3d_pair(ssfa, &tmSFA, leader_full, 0, 8 * kb, mb);
+                    tma_load_3d_pair(ssfb, &tmSFB, leader_full, 0, 8 * kb, rb0);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -344,9 +350,18 @@ int gemm_nvfp4_blocked_pair(const void* Aq, const void* SFA_blocked, const void*
     CUtensorMap tmA, tmB, tmSFA, tmSFB;
     if (!make_tmap_2d_u8(&tmA, Aq, M, K / 2, K / 2, nvfp4p::kBM, nvfp4p::kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
     if (!make_tmap_2d_u8(&tmB, Bq, N, K / 2, K / 2, bn / 2, nvfp4p::kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
-    const uint64_t rows_a = static_cast<uint64_t>((M + 127) / 128) * (K / 64) * 2, rows_b = static_cast<uint64_t>((N + 127) / 128) * (K / 64) * 2;
-    if (!make_tmap_2d_u8(&tmSFA, SFA_blocked, rows_a, 256, 256, 8, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return cudaErrorInvalidValue;
-    if (!make_tmap_2d_u8(&tmSFB, SFB_blocked, rows_b, 256, 256, 8, 256, CU_TENSOR_MAP_SWIZZLE_NONE)) return cudaErrorInvalidValue;
+    {
+        const uint64_t k_rows = static_cast<uint64_t>(K / 64) * 2;                 // 256-byte rows per row block
+        const uint64_t strides[2] = {256, k_rows * 256};
+        const uint64_t dims_a[3] = {256, k_rows, static_cast<uint64_t>((M + 127) / 128)};
+        const uint64_t dims_b[3] = {256, k_rows, static_cast<uint64_t>((N + 127) / 128)};
+        const uint32_t box_a[3] = {256, 8, 1};
+        const uint32_t box_b[3] = {256, 8, static_cast<uint32_t>(bn == 192 ? nvfp4p::Cfg<192>::kNB : nvfp4p::Cfg<256>::kNB)};
+        if (encode_tiled(&tmSFA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, SFA_blocked, dims_a, strides, box_a, CU_TENSOR_MAP_SWIZZLE_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+        if (encode_tiled(&tmSFB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, SFB_blocked, dims_b, strides, box_b, CU_TENSOR_MAP_SWIZZLE_NONE) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
     // C as a bf16 matrix with 32-row x 64-column boxes for the epilogue's stores; when N or the pointer rules
     // out a tensor map (row pitch not a multiple of 16 bytes) the kernel stores element-wise and the map is
     // a never-used placeholder over A.

@@ -101,13 +101,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* status, uint32_t site)
 {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    // The clock is read only every 256 failed polls (a poll itself blocks for a while in hardware), so a
+    // wait that ends soon never pays for reading the global timer.
+    unsigned long long t0 = 0;
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0xFFu) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
-            uint32_t b = blockIdx.x > 0xFFFFFFu ? 0xFFFFFFu : blockIdx.x;
-            atomicCAS(status, 0u, kStatusTimeout | (site << 24) | b);
-            return false;
+        if ((++spins & 0xFFu) == 0) {
+            const unsigned long long now = globaltimer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitLimitNs) {
+                uint32_t b = blockIdx.x > 0xFFFFFFu ? 0xFFFFFFu : blockIdx.x;
+                atomicCAS(status, 0u, kStatusTimeout | (site << 24) | b);
+                return false;
+            }
         }
     }
     return true;
