@@ -226,6 +226,42 @@ def time_loop(fn, iters: int, warm: int = 3):
     return e0.elapsed_time(e1) / iters
 
 
+def _e4m3_normal(rows, cols, gen):
+    """N(0,1) scaled to fit +-448 with one per-tensor scale, as E4M3 bytes (the FP8 GEMM configuration)."""
+    import torch
+    x = torch.randn((rows, cols), device="cuda", generator=gen)
+    scale = float(x.abs().max()) / 448.0
+    return (x / scale).to(torch.float8_e4m3fn).view(torch.uint8), scale
+
+
+def _nvfp4_normal(rows, K, gen):
+    """N(0,1) quantised to NVFP4: E2M1 codes packed two per byte (low nibble = lower K), one UE4M3 scale per
+    16 K (block max-abs / 6, relative to one fp32 global scale), as the NVFP4 configuration states."""
+    import torch
+    x = torch.randn((rows, K // 16, 16), device="cuda", generator=gen)
+    amax = x.abs().amax(-1)
+    glob = float(amax.max()) / (6.0 * 448.0)
+    sf = (amax / 6.0 / glob).to(torch.float8_e4m3fn)
+    y = x / (sf.float() * glob).clamp_min(1e-30).unsqueeze(-1)
+    mids = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], device="cuda")
+    code = torch.bucketize(y.abs(), mids).to(torch.uint8) | ((y < 0).to(torch.uint8) << 3)
+    code = code.view(rows, K)
+    packed = code[:, 0::2] | (code[:, 1::2] << 4)
+    return packed.contiguous(), sf.view(torch.uint8).contiguous(), glob
+
+
+def _sparse24_normal(rows, K, gen):
+    """2:4 sparse A: in every 4 consecutive K two positions chosen uniformly, values N(0,1) as E4M3 with a
+    per-tensor scale; returns the compressed values [rows, K/2], the metadata bytes [rows, K/8] and the scale."""
+    import torch
+    vals, scale = _e4m3_normal(rows, K // 2, gen)
+    pairs = torch.tensor([0b0100, 0b1000, 0b1100, 0b1001, 0b1101, 0b1110], dtype=torch.uint8, device="cuda")  # (p0 | p1 << 2), p0 < p1
+    pick = torch.randint(0, 6, (rows, K // 4), device="cuda", generator=gen)
+    nib = pairs[pick]
+    meta = nib[:, 0::2] | (nib[:, 1::2] << 4)
+    return vals, meta.contiguous(), scale
+
+
 def gemm_cases(peaks):
     """Per-format GEMM numbers (rank 0, N=1): TFLOPS or GB/s and fractions of nominal / measured peaks."""
     import torch
@@ -239,33 +275,33 @@ def gemm_cases(peaks):
     torch.cuda.synchronize(); time.sleep(3.0)
     # FP8 8192^3 (operands 128 MB > L2 is not true here: 2 x 64 MB + 128 MB C; C alone exceeds L2)
     S = 8192
-    a = torch.randint(0, 120, (S, S), dtype=torch.uint8, device="cuda")
-    b = torch.randint(0, 120, (S, S), dtype=torch.uint8, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    a, sa = _e4m3_normal(S, S, gen)
+    b, sb = _e4m3_normal(S, S, gen)
     c = torch.empty((S, S), dtype=torch.bfloat16, device="cuda")
-    ms = time_loop(lambda: L.b200q_gemm_fp8(a.data_ptr(), b.data_ptr(), c.data_ptr(), S, S, S, 1.0, 1.0, st()), 20)
+    ms = time_loop(lambda: L.b200q_gemm_fp8(a.data_ptr(), b.data_ptr(), c.data_ptr(), S, S, S, sa, sb, st()), 20)
     tf = 2 * S ** 3 / ms / 1e9
     out["fp8_8192"] = {"ms": ms, "tflops": tf, "frac_nominal_4500": tf / NOMINAL["fp8_tflops"],
                        "frac_2x_measured_bf16": tf / fp8_meas}
     del a, b, c
     torch.cuda.synchronize(); time.sleep(1.5)
     # NVFP4 8192^3 (scales pre-blocked, as weights would be)
-    A4 = torch.randint(0, 256, (S, S // 2), dtype=torch.uint8, device="cuda")
-    B4 = torch.randint(0, 256, (S, S // 2), dtype=torch.uint8, device="cuda")
-    sf = torch.randint(0x28, 0x48, (L.b200q_nvfp4_sf_bytes(S, S),), dtype=torch.uint8, device="cuda")
+    A4, sfa_rm, ga = _nvfp4_normal(S, S, gen)
+    B4, sfb_rm, gb = _nvfp4_normal(S, S, gen)
+    sfa = ops.nvfp4_swizzle_sf(sfa_rm, S); sfb = ops.nvfp4_swizzle_sf(sfb_rm, S)
     c = torch.empty((S, S), dtype=torch.bfloat16, device="cuda")
-    ms = time_loop(lambda: L.b200q_gemm_nvfp4_blocked(A4.data_ptr(), sf.data_ptr(), B4.data_ptr(), sf.data_ptr(), c.data_ptr(),
-                                                      S, S, S, 1.0, 1.0, st()), 20)
+    ms = time_loop(lambda: L.b200q_gemm_nvfp4_blocked(A4.data_ptr(), sfa.data_ptr(), B4.data_ptr(), sfb.data_ptr(), c.data_ptr(),
+                                                      S, S, S, ga, gb, st()), 20)
     tf = 2 * S ** 3 / ms / 1e9
     out["nvfp4_8192"] = {"ms": ms, "tflops": tf, "frac_nominal_9000": tf / NOMINAL["fp4_tflops"],
                          "frac_4x_measured_bf16": tf / (4.0 * peaks["bf16_tflops"])}
-    del A4, B4, sf
+    del A4, B4, sfa, sfb, sfa_rm, sfb_rm
     torch.cuda.synchronize(); time.sleep(1.5)
     # 2:4 sparse FP8 4096 x 8192 x 8192 (dense-equivalent FLOPs)
     Ms = 4096
-    Ac = torch.randint(0, 120, (Ms, S // 2), dtype=torch.uint8, device="cuda")
-    Em = torch.full((Ms, S // 8), 0xE4, dtype=torch.uint8, device="cuda")
-    Bd = torch.randint(0, 120, (S, S), dtype=torch.uint8, device="cuda")
-    ms = time_loop(lambda: L.b200q_gemm_sp24_fp8(Ac.data_ptr(), Em.data_ptr(), Bd.data_ptr(), c.data_ptr(), Ms, S, S, 1.0, 1.0, st()), 20)
+    Ac, Em, ssa = _sparse24_normal(Ms, S, gen)
+    Bd, ssb = _e4m3_normal(S, S, gen)
+    ms = time_loop(lambda: L.b200q_gemm_sp24_fp8(Ac.data_ptr(), Em.data_ptr(), Bd.data_ptr(), c.data_ptr(), Ms, S, S, ssa, ssb, st()), 20)
     tf = 2 * Ms * S * S / ms / 1e9
     out["sparse_fp8_4096x8192x8192"] = {"ms": ms, "tflops_dense_equivalent": tf, "frac_nominal_dense_4500": tf / NOMINAL["fp8_tflops"],
                                         "frac_nominal_sparse_9000": tf / (2 * NOMINAL["fp8_tflops"])}
