@@ -4,14 +4,15 @@
 // kernel ALU-bound)
 // Bandwidth-bound: one CTA per row, 16-byte streaming loads held in registers across the two
 // passes (row maximum by warp shuffles + shared memory, then convert), 8 bytes written per 8 inputs.
+// The CTA is sized to the row (64 to 256 threads, 8 to 14 vectors each): a row passes through three
+// phases (load, reduce, convert + store) and only the first keeps memory busy, so short rows get small
+// CTAs, many of which are resident per SM in different phases.
 #include "common.cuh"
 #include <cuda_fp8.h>
 #include "../../include/b200q.h"
 
 namespace b200q {
 namespace quant {
-
-constexpr int kThreads = 256;
 
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
@@ -23,12 +24,11 @@ __device__ __forceinline__ uint32_t cvt4_e4m3(float a, float b, float c, float d
     return lo | (hi << 16);
 }
 
-// One CTA per row.  Every thread keeps its share of the row (up to kCache 16-byte vectors = 112
-// values) in registers between the maximum pass and the convert pass, so a row is read from memory
-// once; all of a thread's loads are issued before the first is used.  Longer rows re-read the rest.
-constexpr int kCache = 14;
-
-__global__ void __launch_bounds__(kThreads, 2)
+// One CTA per row.  Every thread keeps its share of the row (up to kCache 16-byte vectors) in registers
+// between the maximum pass and the convert pass, so a row is read from memory once; all of a thread's
+// loads are issued before the first is used.  Rows longer than kThreads * kCache vectors re-read the rest.
+template <int kThreads, int kCache, int kMinCtas>
+__global__ void __launch_bounds__(kThreads, kMinCtas)
 quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict__ Q, float* __restrict__ S, int rows,
                        int cols)
 {
@@ -99,9 +99,15 @@ extern "C" int b200q_quant_rows_e4m3(const void* X, void* Q, float* S, int rows,
     if (!aligned16(X) || (reinterpret_cast<uintptr_t>(Q) & 7u) != 0) return cudaErrorInvalidValue;
     const int sms = num_sms();
     if (sms <= 0) return cudaErrorInvalidDevice;
-    const int grid = rows < sms * 8 ? rows : sms * 8;
-    quant::quant_rows_e4m3_kernel<<<grid, quant::kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __nv_bfloat16*>(X), static_cast<uint8_t*>(Q), S, rows, cols);
+    const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(X);
+    uint8_t* q = static_cast<uint8_t*>(Q);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int vecs = cols / 8;
+    const int grid = rows < sms * 32 ? rows : sms * 32;
+    if (vecs <= 64 * 8) quant::quant_rows_e4m3_kernel<64, 8, 12><<<grid, 64, 0, st>>>(x, q, S, rows, cols);
+    else if (vecs <= 128 * 8) quant::quant_rows_e4m3_kernel<128, 8, 6><<<grid, 128, 0, st>>>(x, q, S, rows, cols);
+    else if (vecs <= 256 * 8) quant::quant_rows_e4m3_kernel<256, 8, 3><<<grid, 256, 0, st>>>(x, q, S, rows, cols);
+    else quant::quant_rows_e4m3_kernel<256, 14, 2><<<grid, 256, 0, st>>>(x, q, S, rows, cols);
     return cudaGetLastError();
 }
 
