@@ -14,7 +14,8 @@
 //   with the per-token sum of the group's activations (which removes the +136 again, in fp32);
 //   one thread issues 8 x tcgen05.mma kind::f16 (128 x 16 x 16), A from TMEM, B from shared memory,
 //   into a per-group fp32 accumulator in TMEM;
-//   the warps read the finished group accumulator (tcgen05.ld) and add
+//   every group has its own accumulator (eight of them), so the warps convert group after group without
+//   waiting for a result, and only at the end read the accumulators (tcgen05.ld) and add
 //   scale[n, group] * (acc - 136 * sum_x) in fp32 registers: q*s is never rounded.
 // Consecutive calls overlap through programmatic dependent launch: a call starts its prologue and
 // weight stream while the previous kernel drains, and waits (griddepcontrol.wait) only before it
@@ -35,16 +36,20 @@ constexpr int kRows = 128;          // weight rows per CTA (UMMA M)
 constexpr int kTok = 16;            // tokens per pass (UMMA N)
 constexpr int kGroup = 128;         // K per scale group
 constexpr int kWStages = 8;         // packed weight tiles in flight (8 KiB each)
-constexpr int kSlots = 2;           // TMEM operand / accumulator slots, activation tiles
+constexpr int kBatch = 3;            // groups converted per hand-off to the MMA thread (one wait, one fence, one arrive)
+constexpr int kASlots = 2 * kBatch;  // TMEM operand slots (64 columns each) with their activation tiles: two batches
+constexpr int kDSlots = 8;          // TMEM accumulators (16 columns each): one per group for up to 8 groups per CTA, so
+                                    // no worker waits for an MMA result before every group has been converted
 constexpr int kWorkers = 256;       // warps 2-9: two threads per weight row (one per 64-K half)
 constexpr int kThreads = 64 + kWorkers;   // warp 0 TMA, warp 1 MMA
 constexpr int kWTileBytes = kRows * 64;
 constexpr int kXTileBytes = 2 * kTok * 128;       // two 64-K sub-tiles of 16 rows x 128 B
-constexpr uint32_t kTmemCols = 256;               // 2 x 64 operand columns + 2 x 16 accumulator columns
-constexpr int kSmemBytes = kWStages * kWTileBytes + kSlots * kXTileBytes + kRows * kTok * 4 + kSlots * kTok * 4 + 1024 + 256;
-// Two CTAs (e.g. the tail of one call and the head of the next, programmatic dependent launch) fit
-// on an SM: shared memory <= half, tensor memory = half.
-static_assert(2 * kSmemBytes <= 227 * 1024, "two CTAs per SM");
+constexpr uint32_t kTmemCols = 512;               // 6 x 64 operand columns + 8 x 16 accumulator columns
+constexpr int kSmemUsed = kWStages * kWTileBytes + kASlots * kXTileBytes + kRows * kTok * 4 + kDSlots * kTok * 4 + 1024 + 256;
+// A CTA takes all 512 TMEM columns, so two CTAs must never share an SM: a second one would block in
+// tcgen05.alloc behind the first, and with clusters waiting on their peers that can close a cycle.
+// Asking for more than half of the SM's shared memory rules it out.
+constexpr int kSmemBytes = kSmemUsed > 120 * 1024 ? kSmemUsed : 120 * 1024;
 
 struct Params {
     const __nv_bfloat16* X;
@@ -105,17 +110,17 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
     const uint32_t w_smem = smem_base;                                   // kWStages x 8 KiB, 64-byte swizzle
-    const uint32_t x_smem = w_smem + kWStages * kWTileBytes;             // kSlots x 4 KiB, 128-byte swizzle
-    const uint32_t red_smem = x_smem + kSlots * kXTileBytes;             // [kTok][kRows] fp32 partial sums
-    const uint32_t sx_smem = red_smem + kRows * kTok * 4;                // [kSlots][kTok] fp32: sum of a group's activations
-    const uint32_t bar_base = sx_smem + kSlots * kTok * 4;
+    const uint32_t x_smem = w_smem + kWStages * kWTileBytes;             // kASlots x 4 KiB, 128-byte swizzle
+    const uint32_t red_smem = x_smem + kASlots * kXTileBytes;            // [kTok][kRows] fp32 partial sums
+    const uint32_t sx_smem = red_smem + kRows * kTok * 4;                // [kDSlots][kTok] fp32: sum of a group's activations
+    const uint32_t bar_base = sx_smem + kDSlots * kTok * 4;
     auto w_full = [&](int s) { return bar_base + 8u * s; };
     auto w_empty = [&](int s) { return bar_base + 8u * (kWStages + s); };
     auto a_ready = [&](int s) { return bar_base + 8u * (2 * kWStages + s); };
-    auto a_free = [&](int s) { return bar_base + 8u * (2 * kWStages + kSlots + s); };
-    auto d_ready = [&](int s) { return bar_base + 8u * (2 * kWStages + 2 * kSlots + s); };
-    auto d_free = [&](int s) { return bar_base + 8u * (2 * kWStages + 3 * kSlots + s); };
-    const uint32_t tmem_slot = bar_base + 8u * (2 * kWStages + 4 * kSlots);
+    auto a_free = [&](int s) { return bar_base + 8u * (2 * kWStages + 2 + s); };          // a_ready / a_free: per batch parity
+    auto d_ready = [&](int s) { return bar_base + 8u * (2 * kWStages + 4 + s); };
+    auto d_free = [&](int s) { return bar_base + 8u * (2 * kWStages + 4 + kDSlots + s); };
+    const uint32_t tmem_slot = bar_base + 8u * (2 * kWStages + 4 + 2 * kDSlots);
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -129,10 +134,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWStages; ++s) { ptx::mbar_init(w_full(s), 1); ptx::mbar_init(w_empty(s), 8); }
-        for (int s = 0; s < kSlots; ++s) {
-            ptx::mbar_init(a_ready(s), 8); ptx::mbar_init(a_free(s), 1);
-            ptx::mbar_init(d_ready(s), 1); ptx::mbar_init(d_free(s), 8);
-        }
+        for (int s = 0; s < 2; ++s) { ptx::mbar_init(a_ready(s), 8); ptx::mbar_init(a_free(s), 1); }
+        for (int s = 0; s < kDSlots; ++s) { ptx::mbar_init(d_ready(s), 1); ptx::mbar_init(d_free(s), 8); }
         ptx::fence_mbar_init();
     }
     if (warp == 1) { ptx::tmem_alloc(tmem_slot, kTmemCols); ptx::tmem_relinquish(); }
@@ -141,8 +144,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
     ptx::tcgen05_fence_after_sync();
     pdl_launch_dependents();        // the next call may begin: its weights do not depend on this call
     const uint32_t tmem_base = *tmem_slot_ptr;
-    const uint32_t a_tmem0 = tmem_base;                       // kSlots x 64 columns: bf16 weights, 2 per column
-    const uint32_t d_tmem0 = tmem_base + kSlots * 64;         // kSlots x 16 columns: fp32 group accumulators
+    const uint32_t a_tmem0 = tmem_base;                       // kASlots x 64 columns: bf16 weights, 2 per column
+    const uint32_t d_tmem0 = tmem_base + kASlots * 64;        // kDSlots x 16 columns: fp32 group accumulators
 
     if (warp == 0) {
         // ------------------------------------------------ TMA: packed weight tiles, independent of X
@@ -163,20 +166,24 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
             // bf16 x bf16 -> fp32, both K-major, M = 128 weight rows, N = 16 tokens
             constexpr uint32_t idesc = ptx::umma_idesc(1, 1, kRows, kTok);
             bool ok = true;
-            for (int i = 0; i < ngroups && ok; ++i) {
-                const int s = i % kSlots;
-                const uint32_t par = (i / kSlots) & 1u;
-                if (!ptx::mbar_wait(a_ready(s), par, p.status, 22)) { ok = false; break; }
-                if (!ptx::mbar_wait(d_free(s), par ^ 1u, p.status, 23)) { ok = false; break; }
-                ptx::tcgen05_fence_after_sync();
-                const uint32_t xs = x_smem + s * kXTileBytes;
+            for (int b = 0; b * kBatch < ngroups && ok; ++b) {
+                const int S = b & 1;
+                if (!ptx::mbar_wait(a_ready(S), (b >> 1) & 1u, p.status, 22)) { ok = false; break; }
+                for (int gi = 0; gi < kBatch && ok; ++gi) {
+                    const int i = b * kBatch + gi;
+                    if (i >= ngroups) break;
+                    const int s = i % kASlots, ds = i % kDSlots;
+                    if (!ptx::mbar_wait(d_free(ds), ((i / kDSlots) & 1u) ^ 1u, p.status, 23)) { ok = false; break; }
+                    ptx::tcgen05_fence_after_sync();
+                    const uint32_t xs = x_smem + s * kXTileBytes;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {       // 16 K per instruction: 8 TMEM columns of A, 32 bytes of B
-                    const uint64_t db = ptx::smem_desc_sw128_kmajor(xs + (j >> 2) * (kTok * 128)) + 2u * (j & 3);
-                    umma_f16_ts(d_tmem0 + s * kTok, a_tmem0 + s * 64 + j * 8, db, idesc, j != 0);
+                    for (int j = 0; j < 8; ++j) {       // 16 K per instruction: 8 TMEM columns of A, 32 bytes of B
+                        const uint64_t db = ptx::smem_desc_sw128_kmajor(xs + (j >> 2) * (kTok * 128)) + 2u * (j & 3);
+                        umma_f16_ts(d_tmem0 + ds * kTok, a_tmem0 + s * 64 + j * 8, db, idesc, j != 0);
+                    }
+                    ptx::umma_commit(d_ready(ds));
                 }
-                ptx::umma_commit(a_free(s));
-                ptx::umma_commit(d_ready(s));
+                if (ok) ptx::umma_commit(a_free(S));
             }
             if (!ok) __nanosleep(200000);
         }
@@ -206,94 +213,127 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
         auto load_scale = [&](int g) {
             return (n < p.N) ? __half2float(__ldg(p.S + static_cast<size_t>(n) * p.groups_total + g)) : 0.0f;
         };
+        // the scales of this CTA's first groups (weights: independent of the previous kernel), all requested now so
+        // that their latencies overlap; the usual case has at most kDSlots groups per CTA and needs no others
+        float scs[kDSlots];
+#pragma unroll
+        for (int j = 0; j < kDSlots; ++j) scs[j] = (j < ngroups) ? load_scale(g_begin + j) : 0.0f;
         pdl_wait();                                            // the activations may come from the previous kernel
-        uint4 xr = make_uint4(0, 0, 0, 0);
-        if (ngroups > 0) xr = load_x(g_begin);
-        float sc_prev = 0.0f;
+        uint4 xr[kBatch];
+#pragma unroll
+        for (int gi = 0; gi < kBatch; ++gi) xr[gi] = (gi < ngroups) ? load_x(g_begin + gi) : make_uint4(0, 0, 0, 0);
 
-        for (int i = 0; i < ngroups && ok; ++i) {
-            const int s = i % kSlots, ws = i % kWStages;
-            const int g = g_begin + i;
-            const float sc_this = load_scale(g);               // used one iteration later: its latency is hidden
-            // slot s (TMEM operand columns + activation tile + sx) is free once the MMAs of group i-kSlots retired
-            // and its accumulator was folded in (iteration i-kSlots+1)
-            if (!ptx::mbar_wait(a_free(s), ((i / kSlots) & 1u) ^ 1u, p.status, 24)) { ok = false; break; }
-            // ... and every worker has folded that group's accumulator in (they read sx[s] doing so)
-            if (!ptx::mbar_wait(d_free(s), ((i / kSlots) & 1u) ^ 1u, p.status, 28)) { ok = false; break; }
+        // accumulator of group i (finished long ago when this is called): sum_k w x = sum_k (136 + w) x - 136 * sum_k x,
+        // times the group's scale, into this thread's fp32 sums
+        auto fold = [&](int i, float sc) -> bool {
+            const int ds = i % kDSlots;
+            if (!ptx::mbar_wait(d_ready(ds), (i / kDSlots) & 1u, p.status, 26)) return false;
             ptx::tcgen05_fence_after_sync();
-            {   // stage this group's activations: K-permuted inside every 8 (x0,x4,x1,x5,x2,x6,x3,x7), 128-byte swizzle;
-                // and the sum of the group's activations per token (for the +136 offset of the weights)
-                uint8_t* xt = smem_gen + (x_smem - smem_base) + s * kXTileBytes;
-                const int h = xq >> 3, xc = xq & 7;
-                const uint32_t off = h * (kTok * 128) + (xm >> 3) * 1024 + (xm & 7) * 128 + ((xc ^ (xm & 7)) << 4);
-                *reinterpret_cast<uint4*>(xt + off) =
-                    make_uint4(__byte_perm(xr.x, xr.z, 0x5410), __byte_perm(xr.x, xr.z, 0x7632),
-                               __byte_perm(xr.y, xr.w, 0x5410), __byte_perm(xr.y, xr.w, 0x7632));
-                const uint32_t w[4] = {xr.x, xr.y, xr.z, xr.w};
-                float t = 0.0f;
+            uint32_t d[8];
+            tmem_ld_32x32b_x8(d_tmem0 + lane_addr + ds * kTok + half * 8, d);
+            ptx::tmem_ld_wait();
+            float sxv[8];
 #pragma unroll
-                for (int k = 0; k < 4; ++k) t += __uint_as_float(w[k] << 16) + __uint_as_float(w[k] & 0xFFFF0000u);
-#pragma unroll
-                for (int o = 8; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);   // the 16 chunks of a token sit in 16 adjacent lanes
-                if (xq == 0) sx[s * kTok + xm] = t;
-            }
-            if (i + 1 < ngroups) xr = load_x(g + 1);           // prefetch the next group's activations
-            // packed weights of this row: this thread converts 32 of its 64 bytes (64-byte-swizzled by TMA)
-            if (!ptx::mbar_wait(w_full(ws), (i / kWStages) & 1u, p.status, 25)) { ok = false; break; }
-            const uint8_t* wt = smem_gen + (w_smem - smem_base) + ws * kWTileBytes + row * 64;
-            const int sw = (row >> 1) & 3;
-#pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {                   // 16 bytes = 32 weights = 16 TMEM columns
-                const int c = 2 * half + cc;
-                const uint4 w4 = *reinterpret_cast<const uint4*>(wt + ((c ^ sw) << 4));
-                const uint32_t ww[4] = {w4.x ^ 0x88888888u, w4.y ^ 0x88888888u, w4.z ^ 0x88888888u, w4.w ^ 0x88888888u};
-                uint32_t r[16];
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {                  // nibble pairs (i, i+4) -> bf16 (136 + w): exact integers
-                    r[4 * k + 0] = (ww[k] & 0x000F000Fu) | 0x43004300u;
-                    r[4 * k + 1] = ((ww[k] >> 4) & 0x000F000Fu) | 0x43004300u;
-                    r[4 * k + 2] = ((ww[k] >> 8) & 0x000F000Fu) | 0x43004300u;
-                    r[4 * k + 3] = ((ww[k] >> 12) & 0x000F000Fu) | 0x43004300u;
-                }
-                tmem_st_32x32b_x16(a_tmem0 + lane_addr + s * 64 + c * 16, r);
-            }
-            tmem_st_wait();
-            ptx::fence_proxy_async_smem();                     // the activation tile was written by ordinary stores
+            for (int m = 0; m < 8; ++m) sxv[m] = sx[ds * kTok + half * 8 + m];
             ptx::tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) { ptx::mbar_arrive(a_ready(s)); ptx::mbar_arrive(w_empty(ws)); }
+            if (lane == 0) ptx::mbar_arrive(d_free(ds));
+#pragma unroll
+            for (int m = 0; m < 8; ++m) acc[m] = fmaf(fmaf(-136.0f, sxv[m], __uint_as_float(d[m])), sc, acc[m]);
+            return true;
+        };
 
-            // fold in the accumulator of the previous group while this group's MMAs run:
-            //   sum_k w x = sum_k (136 + w) x - 136 * sum_k x
-            if (i > 0) {
-                const int sp = (i - 1) % kSlots;
-                if (!ptx::mbar_wait(d_ready(sp), ((i - 1) / kSlots) & 1u, p.status, 26)) { ok = false; break; }
-                ptx::tcgen05_fence_after_sync();
-                uint32_t d[8];
-                tmem_ld_32x32b_x8(d_tmem0 + lane_addr + sp * kTok + half * 8, d);
-                ptx::tmem_ld_wait();
-                float sxv[8];
+        // Groups go to the MMA thread in batches of kBatch: one tcgen05.wait::st, one pair of fences and one
+        // barrier arrival per batch — the hand-off, not the conversion, is what a group costs.
+        for (int b = 0; b * kBatch < ngroups && ok; ++b) {
+            const int S = b & 1;
+            // more than kDSlots groups per CTA: an accumulator (and its sx row) is reused, fold the old one in first
 #pragma unroll
-                for (int m = 0; m < 8; ++m) sxv[m] = sx[sp * kTok + half * 8 + m];
-                ptx::tcgen05_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(d_free(sp));
-#pragma unroll
-                for (int m = 0; m < 8; ++m) acc[m] = fmaf(fmaf(-136.0f, sxv[m], __uint_as_float(d[m])), sc_prev, acc[m]);
+            for (int gi = 0; gi < kBatch; ++gi) {
+                const int i = b * kBatch + gi;
+                if (ok && i < ngroups && i >= kDSlots) {
+                    if (!fold(i - kDSlots, load_scale(g_begin + i - kDSlots))) ok = false;
+                    else if (!ptx::mbar_wait(d_free(i % kDSlots), ((i / kDSlots) & 1u) ^ 1u, p.status, 28)) ok = false;   // every worker has read that sx row
+                }
             }
-            sc_prev = sc_this;
+            if (!ok) break;
+            // the operand slots of this batch parity (TMEM columns + activation tiles) are free once the MMAs of batch b - 2 retired
+            if (!ptx::mbar_wait(a_free(S), ((b >> 1) & 1u) ^ 1u, p.status, 24)) { ok = false; break; }
+            ptx::tcgen05_fence_after_sync();
+#pragma unroll
+            for (int gi = 0; gi < kBatch; ++gi) {
+                const int i = b * kBatch + gi;
+                if (i < ngroups) {
+                    // stage the group's activations: K-permuted inside every 8 (x0,x4,x1,x5,x2,x6,x3,x7), 128-byte swizzle;
+                    // and the sum of the group's activations per token (for the +136 offset of the weights)
+                    uint8_t* xt = smem_gen + (x_smem - smem_base) + (i % kASlots) * kXTileBytes;
+                    const int h = xq >> 3, xc = xq & 7;
+                    const uint32_t off = h * (kTok * 128) + (xm >> 3) * 1024 + (xm & 7) * 128 + ((xc ^ (xm & 7)) << 4);
+                    const uint4 x4 = xr[gi];
+                    *reinterpret_cast<uint4*>(xt + off) =
+                        make_uint4(__byte_perm(x4.x, x4.z, 0x5410), __byte_perm(x4.x, x4.z, 0x7632),
+                                   __byte_perm(x4.y, x4.w, 0x5410), __byte_perm(x4.y, x4.w, 0x7632));
+                    const uint32_t w[4] = {x4.x, x4.y, x4.z, x4.w};
+                    float t = 0.0f;
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) t += __uint_as_float(w[k] << 16) + __uint_as_float(w[k] & 0xFFFF0000u);
+#pragma unroll
+                    for (int o = 8; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);   // the 16 chunks of a token sit in 16 adjacent lanes
+                    if (xq == 0) sx[(i % kDSlots) * kTok + xm] = t;
+                }
+            }
+#pragma unroll
+            for (int gi = 0; gi < kBatch; ++gi) {              // prefetch the next batch's activations
+                const int i = (b + 1) * kBatch + gi;
+                if (i < ngroups) xr[gi] = load_x(g_begin + i);
+            }
+#pragma unroll
+            for (int gi = 0; gi < kBatch; ++gi) {
+                const int i = b * kBatch + gi;
+                if (ok && i < ngroups) {
+                    const int ws = i % kWStages, s = i % kASlots;
+                    // packed weights of this row: this thread converts 32 of its 64 bytes (64-byte-swizzled by TMA)
+                    if (!ptx::mbar_wait(w_full(ws), (i / kWStages) & 1u, p.status, 25)) { ok = false; }
+                    else {
+                        const uint8_t* wt = smem_gen + (w_smem - smem_base) + ws * kWTileBytes + row * 64;
+                        const int sw = (row >> 1) & 3;
+#pragma unroll
+                        for (int cc = 0; cc < 2; ++cc) {                   // 16 bytes = 32 weights = 16 TMEM columns
+                            const int c = 2 * half + cc;
+                            const uint4 w4 = *reinterpret_cast<const uint4*>(wt + ((c ^ sw) << 4));
+                            const uint32_t ww[4] = {w4.x ^ 0x88888888u, w4.y ^ 0x88888888u, w4.z ^ 0x88888888u, w4.w ^ 0x88888888u};
+                            uint32_t r[16];
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {                  // nibble pairs (i, i+4) -> bf16 (136 + w): exact integers
+                                r[4 * k + 0] = (ww[k] & 0x000F000Fu) | 0x43004300u;
+                                r[4 * k + 1] = ((ww[k] >> 4) & 0x000F000Fu) | 0x43004300u;
+                                r[4 * k + 2] = ((ww[k] >> 8) & 0x000F000Fu) | 0x43004300u;
+                                r[4 * k + 3] = ((ww[k] >> 12) & 0x000F000Fu) | 0x43004300u;
+                            }
+                            tmem_st_32x32b_x16(a_tmem0 + lane_addr + s * 64 + c * 16, r);
+                        }
+                    }
+                }
+            }
+            if (!ok) break;
+            tmem_st_wait();
+            ptx::fence_proxy_async_smem();                     // the activation tiles were written by ordinary stores
+            ptx::tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                ptx::mbar_arrive(a_ready(S));
+                for (int gi = 0; gi < kBatch; ++gi)
+                    if (b * kBatch + gi < ngroups) ptx::mbar_arrive(w_empty((b * kBatch + gi) % kWStages));
+            }
         }
-        if (ok && ngroups > 0) {
-            const int il = ngroups - 1, sp = il % kSlots;
-            if (ptx::mbar_wait(d_ready(sp), (il / kSlots) & 1u, p.status, 27)) {
-                ptx::tcgen05_fence_after_sync();
-                uint32_t d[8];
-                tmem_ld_32x32b_x8(d_tmem0 + lane_addr + sp * kTok + half * 8, d);
-                ptx::tmem_ld_wait();
+        // the accumulators still in tensor memory (all of them when the CTA has at most kDSlots groups)
+        if (ngroups <= kDSlots) {
 #pragma unroll
-                for (int m = 0; m < 8; ++m)
-                    acc[m] = fmaf(fmaf(-136.0f, sx[sp * kTok + half * 8 + m], __uint_as_float(d[m])), sc_prev, acc[m]);
-            }
+            for (int j = 0; j < kDSlots; ++j)
+                if (ok && j < ngroups && !fold(j, scs[j])) ok = false;
+        } else {
+            for (int i = ngroups - kDSlots; i < ngroups && ok; ++i)
+                if (!fold(i, load_scale(g_begin + i))) ok = false;
         }
         // partial sums of this K slice: [token][row] so that the cluster reduction reads rows contiguously
         float* red = reinterpret_cast<float*>(smem_gen + (red_smem - smem_base));

@@ -22,10 +22,13 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=16)
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--nvfp4-pair", type=int, default=-1, help="1/0: force the CTA-pair / one-CTA NVFP4 kernel")
+    ap.add_argument("--w4a16-impl", type=int, default=-1, help="b200q_w4a16_set_impl value for the w4a16 case")
     a = ap.parse_args()
     L = ops.lib()
     if a.nvfp4_pair >= 0:
         L.b200q_nvfp4_set_2cta(a.nvfp4_pair)
+    if a.w4a16_impl >= 0:
+        L.b200q_w4a16_set_impl(a.w4a16_impl)
     st = torch.cuda.current_stream().cuda_stream
     S = a.size
     u8 = lambda *shape, hi=120: torch.randint(0, hi, shape, dtype=torch.uint8, device="cuda")
