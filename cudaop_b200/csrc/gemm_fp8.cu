@@ -9,6 +9,7 @@ namespace fp8 {
 namespace {
 
 int g_force_bn = 0;      // 0 = choose per problem; 224 or 256 = forced (b200q_fp8_set_tile_n)
+int g_pair_group = 0;    // CTA-pair kernels: tile rows (of 256) that walk the N tiles together; 0 = by L2 footprint (b200q_fp8_set_group)
 int g_reducer_stride = 1;
 int g_sm_limit = 0;       // 0 = all SMs; otherwise the persistent grids use at most this many (b200q_fp8_set_sm_limit)
 
@@ -163,7 +164,7 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
         CUtensorMap tA, tB, tB2;
         p.tiles_m = (M + kPairBM - 1) / kPairBM;
         p.tiles_n = (N + oc - 1) / oc;
-        p.group = 8;
+        p.group = g_pair_group > 0 ? g_pair_group : choose_tile_group(p.tiles_m, kPairBM, static_cast<size_t>(K));
         if (!make_tmap_2d_u8(&tA, A, M, K, K, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
         if (!make_tmap_2d_u8(&tB, B, N, K, K, pbn / 2, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
         tB2 = tB;
@@ -279,6 +280,13 @@ int b200q_fp8_set_sm_limit(int sms)
 int b200q_fp8_set_2cta(int on)
 {
     b200q::fp8::g_use_2cta = on ? 1 : 0;
+    return 0;
+}
+
+int b200q_fp8_set_group(int g)
+{
+    if (g < 0 || g > 64) return cudaErrorInvalidValue;
+    b200q::fp8::g_pair_group = g;
     return 0;
 }
 

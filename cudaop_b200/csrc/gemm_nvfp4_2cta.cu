@@ -51,12 +51,12 @@ struct Params {
     __nv_bfloat16* C;
     float alpha;
     int tiles_m, tiles_n;
+    int group;                   // tile rows (of 256) that walk the N tiles together
     uint32_t* status;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn)
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int kGroup, int& tm, int& tn)
 {
-    constexpr int kGroup = 8;
     const int per_group = kGroup * tiles_n;
     const int g = tile / per_group;
     const int first = g * kGroup;
@@ -145,7 +145,7 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
             ptx::tma_prefetch_desc(&tmSFA); ptx::tma_prefetch_desc(&tmSFB);
             int stage = 0; uint32_t phase = 0; bool ok = true;
             for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
-                int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
                 const int m0 = tm * (2 * kBM) + static_cast<int>(cta_rank) * kBM;
                 const int n0 = tn * BN;
                 const int rb0 = n0 / 128;
@@ -178,7 +178,7 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 const uint32_t par = (C::kAccBufs == 2) ? ((t >> 1) & 1u) : (t & 1u);
                 if (!ptx::mbar_wait(tempty_bar(buf), par ^ 1u, p.status, 2)) { ok = false; break; }
                 ptx::tcgen05_fence_after_sync();
-                int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
                 const uint32_t sfb_col_off = ((tn * BN) % 128) / 32;
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -230,7 +230,7 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
             const int buf = (C::kAccBufs == 2) ? (t & 1) : 0;
             const uint32_t par = (C::kAccBufs == 2) ? ((t >> 1) & 1u) : (t & 1u);
-            int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
             const int row0 = tm * (2 * kBM) + static_cast<int>(cta_rank) * kBM + q * 32;
             const int row = row0 + lane;
             const int n0 = tn * BN + col_begin;
@@ -333,6 +333,13 @@ cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
 }  // namespace nvfp4p
 }  // namespace b200q
 
+namespace b200q { namespace nvfp4p { int g_group = 0; } }     // 0 = by L2 footprint
+extern "C" int b200q_nvfp4_set_group(int g)
+{
+    if (g < 0 || g > 64) return cudaErrorInvalidValue;
+    b200q::nvfp4p::g_group = g;
+    return 0;
+}
 // Called by b200q_gemm_nvfp4_blocked when the CTA-pair kernel is selected (b200q_nvfp4_set_2cta).
 namespace b200q {
 int gemm_nvfp4_blocked_pair(const void* Aq, const void* SFA_blocked, const void* Bq, const void* SFB_blocked,
@@ -347,6 +354,8 @@ int gemm_nvfp4_blocked_pair(const void* Aq, const void* SFA_blocked, const void*
     p.M = M; p.N = N; p.K = K; p.C = static_cast<__nv_bfloat16*>(C); p.alpha = global_a * global_b;
     p.status = status_ptr();
     if (p.status == nullptr) return cudaErrorInvalidDevice;
+    p.group = nvfp4p::g_group > 0 ? nvfp4p::g_group
+                                  : choose_tile_group((M + 2 * nvfp4p::kBM - 1) / (2 * nvfp4p::kBM), 2 * nvfp4p::kBM, static_cast<size_t>(K) / 2);
     CUtensorMap tmA, tmB, tmSFA, tmSFB;
     if (!make_tmap_2d_u8(&tmA, Aq, M, K / 2, K / 2, nvfp4p::kBM, nvfp4p::kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
     if (!make_tmap_2d_u8(&tmB, Bq, N, K / 2, K / 2, bn / 2, nvfp4p::kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
