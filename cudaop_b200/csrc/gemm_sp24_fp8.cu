@@ -30,8 +30,9 @@ struct Cfg {
     static constexpr int kBHalf = BN * 128;              // one 128-logical-K tile of B
     static constexpr int kMetaBytes = 2 * kBM * 16;      // two [128][16 B] boxes
     static constexpr int kStageBytes = kABytes + 2 * kBHalf + kMetaBytes;
-    static constexpr int kStages = (227 * 1024 - 1024 - 256) / kStageBytes;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kStoreBytes = 4 * 2 * 2048;     // per epilogue warp two 32-row x 32-column bf16 staging buffers
+    static constexpr int kStages = (227 * 1024 - 1024 - 256 - kStoreBytes) / kStageBytes;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
     static constexpr int kAccBufs = 2 * BN + 8 <= 512 ? 2 : 1;
     static constexpr int kMetaCol = kAccBufs * BN;
     static_assert(kStageBytes % 1024 == 0, "stage alignment");
@@ -43,12 +44,13 @@ struct Params {
     __nv_bfloat16* C;
     float alpha;
     int tiles_m, tiles_n;
+    int group;                   // tile rows that walk the N tiles together
+    int tma_store;               // bf16 results leave through TMA stores (tensor map valid)
     uint32_t* status;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn)
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int kGroup, int& tm, int& tn)
 {
-    constexpr int kGroup = 16;
     const int per_group = kGroup * tiles_n;
     const int g = tile / per_group;
     const int first = g * kGroup;
@@ -61,13 +63,14 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sp24_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmE,
-                     const __grid_constant__ CUtensorMap tmB, const Params p)
+                     const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, const Params p)
 {
     using C = Cfg<BN>;
     constexpr int kStages = C::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bar_base = smem_base + kStages * C::kStageBytes;
+    const uint32_t store_base = smem_base + kStages * C::kStageBytes;      // epilogue staging (1024-byte aligned)
+    const uint32_t bar_base = store_base + C::kStoreBytes;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
@@ -96,7 +99,7 @@ gemm_sp24_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             ptx::tma_prefetch_desc(&tmA); ptx::tma_prefetch_desc(&tmE); ptx::tma_prefetch_desc(&tmB);
             int stage = 0; uint32_t phase = 0; bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+                int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
                 const int m0 = tm * kBM, n0 = tn * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, p.status, 1)) { ok = false; break; }
@@ -154,14 +157,21 @@ gemm_sp24_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             if (!ok) __nanosleep(200000);
         }
     } else {
+        // Each warp owns 32 accumulator rows; 32 columns at a time: tensor memory -> registers -> bf16 in a
+        // 64-byte-swizzled staging buffer -> one TMA store of the 32 x 32 box (clipped at the matrix edge by the
+        // tensor map, evict-first in L2).  Without a usable tensor map: 16-byte stores per thread.
         const int q = warp & 3;
         const bool vec_ok = ((static_cast<long long>(p.N) * 2) % 16 == 0) && aligned16(p.C);
+        const uint32_t stage_buf = store_base + static_cast<uint32_t>(q) * 4096u;
+        const uint64_t store_policy = ptx::l2_policy_evict_first();
+        uint32_t chunk_no = 0;
         int t = 0; bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
             const int buf = (C::kAccBufs == 2) ? (t & 1) : 0;
             const uint32_t par = (C::kAccBufs == 2) ? ((t >> 1) & 1u) : (t & 1u);
-            int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-            const int row = tm * kBM + q * 32 + lane;
+            int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
+            const int row0 = tm * kBM + q * 32;
+            const int row = row0 + lane;
             const int n0 = tn * BN;
             if (!ptx::mbar_wait(tfull_bar(buf), par, p.status, 4)) { ok = false; break; }
             ptx::tcgen05_fence_after_sync();
@@ -171,21 +181,43 @@ gemm_sp24_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
                 ptx::tmem_ld_wait();
+                if (c == BN / 32 - 1) {           // last columns read: the accumulator goes back to the MMA thread
+                    ptx::tcgen05_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+                }
                 const int col0 = n0 + c * 32;
-                if (row < p.M && col0 < p.N) {
+                if (row0 >= p.M || col0 >= p.N) continue;
+                uint4 o[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    o[i].x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * p.alpha, __uint_as_float(r[8 * i + 1]) * p.alpha);
+                    o[i].y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * p.alpha, __uint_as_float(r[8 * i + 3]) * p.alpha);
+                    o[i].z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * p.alpha, __uint_as_float(r[8 * i + 5]) * p.alpha);
+                    o[i].w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * p.alpha, __uint_as_float(r[8 * i + 7]) * p.alpha);
+                }
+                if (p.tma_store) {
+                    const uint32_t sbuf = stage_buf + (chunk_no & 1u) * 2048u;
+                    ++chunk_no;
+                    if (lane == 0) ptx::tma_store_wait_read<1>();     // the store that last read this buffer has finished reading
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t off = lane * 64u + j * 16u;
+                        const uint32_t phys = off ^ (((off >> 7) & 3u) << 4);           // 64-byte swizzle
+                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbuf + phys), "r"(o[j].x), "r"(o[j].y),
+                                     "r"(o[j].z), "r"(o[j].w) : "memory");
+                    }
+                    ptx::fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) { ptx::tma_store_2d_hint(&tmC, sbuf, col0, row0, store_policy); ptx::tma_store_commit(); }
+                } else if (row < p.M) {
                     __nv_bfloat16* dst = p.C + static_cast<size_t>(row) * p.N + col0;
                     const int valid = min(32, p.N - col0);
                     if (vec_ok && valid == 32) {
                         uint4* d = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            uint4 o;
-                            o.x = pack_bf16x2(__uint_as_float(r[8 * i + 0]) * p.alpha, __uint_as_float(r[8 * i + 1]) * p.alpha);
-                            o.y = pack_bf16x2(__uint_as_float(r[8 * i + 2]) * p.alpha, __uint_as_float(r[8 * i + 3]) * p.alpha);
-                            o.z = pack_bf16x2(__uint_as_float(r[8 * i + 4]) * p.alpha, __uint_as_float(r[8 * i + 5]) * p.alpha);
-                            o.w = pack_bf16x2(__uint_as_float(r[8 * i + 6]) * p.alpha, __uint_as_float(r[8 * i + 7]) * p.alpha);
-                            d[i] = o;
-                        }
+                        for (int i = 0; i < 4; ++i) d[i] = o[i];
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i)
@@ -193,10 +225,8 @@ gemm_sp24_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     }
                 }
             }
-            ptx::tcgen05_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
         }
+        if (lane == 0) ptx::tma_store_wait_all<0>();       // shared memory must outlive the stores that read it
     }
 
     ptx::tcgen05_fence_before_sync();
@@ -208,7 +238,7 @@ gemm_sp24_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 }
 
 template <int BN>
-cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmE, const CUtensorMap& tmB, Params p,
+cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmE, const CUtensorMap& tmB, const CUtensorMap& tmC, Params p,
                    cudaStream_t stream)
 {
     auto kernel = gemm_sp24_fp8_kernel<BN>;
@@ -223,10 +253,11 @@ cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmE, const CUtenso
     }
     p.tiles_m = (p.M + kBM - 1) / kBM;
     p.tiles_n = (p.N + BN - 1) / BN;
+    p.group = choose_tile_group(p.tiles_m, kBM, static_cast<size_t>(p.K) / 2);     // compressed A rows of a group stay in L2
     const int sms = num_sms();
     if (sms <= 0) return cudaErrorInvalidDevice;
     const int tiles = p.tiles_m * p.tiles_n;
-    kernel<<<tiles < sms ? tiles : sms, kThreads, Cfg<BN>::kSmemBytes, stream>>>(tmA, tmE, tmB, p);
+    kernel<<<tiles < sms ? tiles : sms, kThreads, Cfg<BN>::kSmemBytes, stream>>>(tmA, tmE, tmB, tmC, p);
     return cudaGetLastError();
 }
 
@@ -260,10 +291,22 @@ int b200q_gemm_sp24_fp8(const void* Acomp, const void* Ameta, const void* B, voi
     if (!make_tmap_2d_u8(&tmA, Acomp, M, K / 2, K / 2, sp24::kBM, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
     if (!make_tmap_2d_u8(&tmE, Ameta, M, K / 8, K / 8, sp24::kBM, 16, CU_TENSOR_MAP_SWIZZLE_NONE)) return cudaErrorInvalidValue;
     if (!make_tmap_2d_u8(&tmB, B, N, K, K, bn, 128, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
+    // C as a bf16 matrix with the epilogue's 32 x 32 boxes; a row pitch that is not a multiple of 16 bytes rules the
+    // tensor map out, and the kernel then stores from registers
+    CUtensorMap tmC = tmA;
+    p.tma_store = 0;
+    if ((static_cast<long long>(N) * 2) % 16 == 0 && aligned16(C)) {
+        const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(N) * 2};
+        const uint32_t box[2] = {32, 32};
+        if (encode_tiled(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B) != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+        p.tma_store = 1;
+    }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (bn == 128) return sp24::launch<128>(tmA, tmE, tmB, p, s);
-    if (bn == 256) return sp24::launch<256>(tmA, tmE, tmB, p, s);
-    return sp24::launch<192>(tmA, tmE, tmB, p, s);
+    if (bn == 128) return sp24::launch<128>(tmA, tmE, tmB, tmC, p, s);
+    if (bn == 256) return sp24::launch<256>(tmA, tmE, tmB, tmC, p, s);
+    return sp24::launch<192>(tmA, tmE, tmB, tmC, p, s);
 }
 
 }  // extern "C"

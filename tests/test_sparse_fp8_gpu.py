@@ -59,7 +59,8 @@ def test_all_six_position_pairs_exact(tile_n):
     assert np.array_equal(bf16_to_f32(out), oracle.decode_bf16(oracle.encode_bf16(A @ B.T)))
 
 
-@pytest.mark.parametrize("shape", [(1, 8, 128), (128, 192, 128), (130, 200, 384), (300, 520, 896), (512, 1024, 2048)])
+@pytest.mark.parametrize("shape", [(1, 8, 128), (128, 192, 128), (130, 200, 384), (260, 100, 256), (300, 520, 896),
+                                   (512, 1024, 2048), (4100, 260, 512)])
 def test_quantised_normal_operands(tile_n, shape):
     import cudaop_b200 as ops
     M, N, K = shape
