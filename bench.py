@@ -519,8 +519,8 @@ def run_ours(args):
                      "flops_per_launch": top_flops,
                      # dram__bytes_read.sum + dram__bytes_write.sum of this kernel at tp1 from one ncu capture
                      # (profiles/gemm_fp8_2cta_kernel_swiglu_mlp_gate_up.txt); algorithmic minimum 739 MB
-                     "traffic": 1202273024 if world == 1 else None,
-                     "tensor_pipe_active_pct_ncu": 91.9 if world == 1 else None},
+                     "traffic": 822281472 if world == 1 else None,
+                     "tensor_pipe_active_pct_ncu": 91.0 if world == 1 else None},
     }
     if world == 1 and not args.no_cases:
         line["cases"] = gemm_cases(peaks)
