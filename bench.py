@@ -283,6 +283,17 @@ def gemm_cases(peaks):
     tf = 2 * S ** 3 / ms / 1e9
     out["fp8_8192"] = {"ms": ms, "tflops": tf, "frac_nominal_4500": tf / NOMINAL["fp8_tflops"],
                        "frac_2x_measured_bf16": tf / fp8_meas}
+    # the same kernel on operands of lower switching activity (uniform bytes in [0,120): positive, all exponents):
+    # the part runs at its power cap, so the operand statistics set the clock and with it the TFLOPS
+    torch.cuda.synchronize(); time.sleep(1.5)
+    a.copy_(torch.randint(0, 120, (S, S), dtype=torch.uint8, device="cuda", generator=gen))
+    b.copy_(torch.randint(0, 120, (S, S), dtype=torch.uint8, device="cuda", generator=gen))
+    torch.cuda.synchronize(); time.sleep(1.0)
+    ms = time_loop(lambda: L.b200q_gemm_fp8(a.data_ptr(), b.data_ptr(), c.data_ptr(), S, S, S, 1.0, 1.0, st()), 20)
+    tf = 2 * S ** 3 / ms / 1e9
+    out["fp8_8192_uniform_bytes"] = {"ms": ms, "tflops": tf, "frac_nominal_4500": tf / NOMINAL["fp8_tflops"],
+                                     "frac_2x_measured_bf16": tf / fp8_meas,
+                                     "note": "not the configuration's distribution: shows the power-cap effect of the data"}
     del a, b, c
     torch.cuda.synchronize(); time.sleep(1.5)
     # NVFP4 8192^3 (scales pre-blocked, as weights would be)
