@@ -47,6 +47,7 @@ _SIGNATURES = {
     "b200q_fp8_set_tma_store": [_I],
     "b200q_fp8_set_group": [_I],
     "b200q_nvfp4_set_group": [_I],
+    "b200q_sp24_set_2cta": [_I],
     "b200q_w4a16_set_impl": [_I],
     "b200q_w4a16_set_pdl": [_I],
     "b200q_sp24_set_tile_n": [_I],

@@ -262,11 +262,23 @@ cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmE, const CUtenso
 }
 
 int g_tile_n = 192;
+int g_use_2cta = 1;      // 1 (default): CTA-pair kernel (gemm_sp24_fp8_2cta.cu, 256 x 224 tiles) for M > 128 (b200q_sp24_set_2cta)
 
 }  // namespace sp24
 }  // namespace b200q
 
+namespace b200q {
+// gemm_sp24_fp8_2cta.cu
+int gemm_sp24_fp8_pair(const void* Acomp, const void* Ameta, const void* B, void* C, int M, int N, int K, float alpha, void* stream);
+}
+
 extern "C" {
+
+int b200q_sp24_set_2cta(int on)
+{
+    b200q::sp24::g_use_2cta = on ? 1 : 0;
+    return 0;
+}
 
 int b200q_sp24_set_tile_n(int bn)
 {
@@ -282,6 +294,7 @@ int b200q_gemm_sp24_fp8(const void* Acomp, const void* Ameta, const void* B, voi
     if (Acomp == nullptr || Ameta == nullptr || B == nullptr || C == nullptr) return cudaErrorInvalidValue;
     if (M <= 0 || N <= 0 || K <= 0 || K % 128 != 0) return cudaErrorInvalidValue;
     if (!aligned16(Acomp) || !aligned16(Ameta) || !aligned16(B)) return cudaErrorInvalidValue;
+    if (sp24::g_use_2cta && M > sp24::kBM) return gemm_sp24_fp8_pair(Acomp, Ameta, B, C, M, N, K, scale_a * scale_b, stream);
     sp24::Params p{};
     p.M = M; p.N = N; p.K = K; p.C = static_cast<__nv_bfloat16*>(C); p.alpha = scale_a * scale_b;
     p.status = status_ptr();

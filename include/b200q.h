@@ -119,6 +119,7 @@ int b200q_w4a16_set_pdl(int on);        /* programmatic dependent launch of the 
                                          * the call may start streaming its weights while the previous kernel of the stream
                                          * still runs, so that kernel must not be the one that writes Wq or S */
 int b200q_sp24_set_tile_n(int bn);
+int b200q_sp24_set_2cta(int on);       /* 2:4-sparse GEMM on CTA pairs (256 x 224 tiles) when M > 128; default on */
 
 /* Activation quantiser: X[rows,cols] bf16 -> Q[rows,cols] E4M3 and S[rows] fp32,
  * S[r] = max|X[r,:]| / 448 (1 for a zero row), Q = rn_satfinite(X * (1 / S[r])).  No counterpart in

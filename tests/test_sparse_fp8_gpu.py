@@ -10,12 +10,17 @@ from tests.util import CORES, assert_bar, bf16_to_f32, dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=[128, 192, 256])
+@pytest.fixture(params=[(128, 0), (192, 0), (256, 0), (192, 1)], ids=["one_cta_128", "one_cta_192", "one_cta_256", "cta_pair_224"])
 def tile_n(request):
+    """Every kernel variant: one-CTA tiles of 128/192/256 columns, and the CTA-pair kernel (256 x 224 tiles; problems of
+    at most 128 rows still go to the one-CTA kernel)."""
     import cudaop_b200 as ops
-    ops.lib().b200q_sp24_set_tile_n(request.param)
-    yield request.param
+    bn, pair = request.param
+    ops.lib().b200q_sp24_set_tile_n(bn)
+    ops.lib().b200q_sp24_set_2cta(pair)
+    yield bn
     ops.lib().b200q_sp24_set_tile_n(192)
+    ops.lib().b200q_sp24_set_2cta(1)
 
 
 def _ref(comp, meta, bq, sa, sb):
