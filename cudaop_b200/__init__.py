@@ -21,7 +21,7 @@ _lib = None
 
 __all__ = [
     "lib", "gemm_fp8", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "gemm_nvfp4", "nvfp4_swizzle_sf",
-    "gemm_sparse_fp8", "quant_rows_e4m3", "status", "LIB_PATH",
+    "gemm_sparse_fp8", "quant_rows_e4m3", "status", "check_status", "set_wait_limit_ms", "WaitTimeout", "LIB_PATH",
 ]
 
 _VP, _I, _F = C.c_void_p, C.c_int, C.c_float
@@ -54,6 +54,10 @@ _SIGNATURES = {
     "b200q_gemm_sp24_fp8": [_VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
     "b200q_quant_rows_e4m3": [_VP, _VP, _VP, _I, _I, _VP],
     "b200q_status": [_VP, _I],
+    "b200q_set_wait_limit_ms": [_I, _I],
+    "b200q_allreduce_to_bf16_one_device": [_VP, _VP, _VP, _I, C.c_longlong, C.c_longlong, _I, C.c_uint, C.c_uint, _I, _VP],
+    "b200q_gemm_fp8_rowcol_allreduce_one_device": [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I,
+                                                   C.c_uint, C.c_uint, _I, _I, _VP],
     "b200q_gemm_fp8_rowcol_allreduce": [_VP, _VP, _VP, _I, _I, _I, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _VP,
                                         C.c_uint, C.c_uint, _I, _I, _VP],
     "b200q_fp8_set_tile_n": [_I],
@@ -256,7 +260,25 @@ def quant_rows_e4m3(x: torch.Tensor):
 
 
 def status(clear: bool = True) -> int:
-    """Device status word: 0 unless a kernel gave up on a bounded wait."""
+    """Device status word: 0 unless a kernel gave up on a bounded wait (then its output is undefined)."""
     v = C.c_uint(0)
     _raise(lib().b200q_status(C.byref(v), int(clear)), "b200q_status")
     return v.value
+
+
+def set_wait_limit_ms(ms: int, cross_rank: bool = False) -> None:
+    """Limit of the kernels' bounded waits on the current device (inside the GPU, or on another rank's flags)."""
+    _raise(lib().b200q_set_wait_limit_ms(int(cross_rank), int(ms)), "b200q_set_wait_limit_ms")
+
+
+class WaitTimeout(RuntimeError):
+    """A kernel gave up on a bounded wait; the outputs of that call are undefined."""
+
+
+def check_status(what: str = "") -> None:
+    """Synchronises the current device and raises WaitTimeout if any kernel gave up on a bounded wait."""
+    w = status(clear=True)
+    if w:
+        site, cta = (w >> 24) & 0x7F, w & 0xFFFFFF
+        raise WaitTimeout(f"{what + ': ' if what else ''}a kernel gave up waiting (site {site}, CTA {cta}); "
+                          "its output is undefined")

@@ -43,45 +43,33 @@ using arc::st_release_sys;
 using arc::ld_acquire_sys;
 
 // Barrier between the CTAs with the same index on every rank.  Flags: pad[phase][cta][src_rank].
-// Returns false if a peer did not arrive within the wait limit.
-__device__ __forceinline__ bool rank_barrier(const Params& p, int phase, bool& ok_shared_unused)
+// Returns false (for the whole CTA) if a peer did not arrive within the cross-rank wait limit.
+__device__ __forceinline__ bool rank_barrier(const Params& p, int phase, int cta)
 {
     __syncthreads();
     bool ok = true;
     if (threadIdx.x < p.world) {
         const int peer = threadIdx.x;
-        const size_t slot = p.pad_offset_words + (static_cast<size_t>(phase) * kMaxCtas + blockIdx.x) * kMaxWorld;
+        const size_t slot = p.pad_offset_words + (static_cast<size_t>(phase) * kMaxCtas + cta) * kMaxWorld;
         __threadfence_system();
         st_release_sys(p.signal_ptrs[peer] + slot + p.rank, p.epoch);
-        const uint32_t* mine = p.signal_ptrs[p.rank] + slot + peer;
-        const unsigned long long t0 = ptx::globaltimer_ns();
-        uint32_t spins = 0;
-        // flags only grow; the signed difference tolerates wrap-around of the epoch counter
-        while (static_cast<int32_t>(ld_acquire_sys(mine) - p.epoch) < 0) {
-            if ((++spins & 0x3Fu) == 0 && ptx::globaltimer_ns() - t0 > ptx::kWaitLimitNs) {
-                atomicCAS(p.status, 0u, ptx::kStatusTimeout | ((16u + phase) << 24) | (blockIdx.x & 0xFFFFFFu));
-                ok = false;
-                break;
-            }
-        }
+        ok = arc::wait_flag(p.signal_ptrs[p.rank] + slot + peer, p.epoch, p.status, 16u + phase);
     }
-    (void)ok_shared_unused;
     return __syncthreads_and(ok);
 }
 
+// The work of CTA `cta` of `nctas` on rank p.rank.
 template <bool MC, bool PartialBf16, int UNROLL>
-__global__ void __launch_bounds__(kThreads)
-allreduce_to_bf16_kernel(const Params p)
+__device__ __forceinline__ void allreduce_body(const Params& p, int cta, int nctas)
 {
-    const int kThreads = blockDim.x;          // 128..512: small blocks on every SM disturb a co-running GEMM evenly
-    bool dummy = true;
-    if (!rank_barrier(p, 0, dummy)) return;
+    const int nthreads = blockDim.x;          // 128..512: small blocks on every SM disturb a co-running GEMM evenly
+    if (!rank_barrier(p, 0, cta)) return;
 
     const long long per = p.elems / p.world;                 // elements this rank reduces
     const long long base = p.offset + per * p.rank;
     const long long vecs = per / 8;                           // 8 values in -> 8 bf16 (16 bytes) out
-    const long long stride = static_cast<long long>(gridDim.x) * kThreads;
-    for (long long vb = blockIdx.x * static_cast<long long>(kThreads) + threadIdx.x; vb < vecs; vb += stride * UNROLL) {
+    const long long stride = static_cast<long long>(nctas) * nthreads;
+    for (long long vb = cta * static_cast<long long>(nthreads) + threadIdx.x; vb < vecs; vb += stride * UNROLL) {
         uint4 o[UNROLL];
         long long e[UNROLL];
         bool valid[UNROLL];
@@ -93,7 +81,26 @@ allreduce_to_bf16_kernel(const Params p)
         for (int u = 0; u < UNROLL; ++u)
             if (valid[u]) arc::broadcast8<MC>(p.out_ptrs, p.out_mc, p.world, e[u], o[u]);
     }
-    rank_barrier(p, 1, dummy);
+    rank_barrier(p, 1, cta);
+}
+
+template <bool MC, bool PartialBf16, int UNROLL>
+__global__ void __launch_bounds__(kThreads)
+allreduce_to_bf16_kernel(const Params p)
+{
+    allreduce_body<MC, PartialBf16, UNROLL>(p, blockIdx.x, gridDim.x);
+}
+
+// Every rank of a small world inside ONE launch on ONE device: CTAs [r * ctas, (r + 1) * ctas) play rank r on
+// that rank's buffers (all in this device's memory).  The launch is cooperative, so all CTAs are resident at
+// once and the flag protocol between the "ranks" makes progress; separate launches that wait on one another
+// on one device would have no such guarantee.  Peer loads/stores only.
+template <bool PartialBf16>
+__global__ void __launch_bounds__(kThreads)
+allreduce_one_device_kernel(Params p, int ctas_per_rank)
+{
+    p.rank = blockIdx.x / ctas_per_rank;
+    allreduce_body<false, PartialBf16, 2>(p, blockIdx.x % ctas_per_rank, ctas_per_rank);
 }
 
 int g_unroll = 4;
@@ -146,6 +153,31 @@ int b200q_allreduce_to_bf16(const void* const* partial_ptrs_dev, void* const* ou
 #undef B200Q_AR_U
 #undef B200Q_AR
     return cudaGetLastError();
+}
+
+int b200q_allreduce_to_bf16_one_device(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                       void* const* signal_ptrs_dev, int partial_is_bf16, long long elem_offset,
+                                       long long elems, int world, unsigned int epoch, unsigned int signal_offset_bytes,
+                                       int ctas_per_rank, void* stream)
+{
+    using namespace b200q;
+    if (partial_ptrs_dev == nullptr || out_ptrs_dev == nullptr || signal_ptrs_dev == nullptr) return cudaErrorInvalidValue;
+    if (world < 1 || world > ar::kMaxWorld) return cudaErrorInvalidValue;
+    if (elems <= 0 || elem_offset < 0 || elems % (8LL * world) != 0 || elem_offset % 8 != 0) return cudaErrorInvalidValue;
+    if (ctas_per_rank < 1 || ctas_per_rank > ar::kMaxCtas || signal_offset_bytes % 4 != 0) return cudaErrorInvalidValue;
+    ar::Params p{};
+    p.partial_ptrs = reinterpret_cast<const float* const*>(partial_ptrs_dev);
+    p.out_ptrs = reinterpret_cast<__nv_bfloat16* const*>(out_ptrs_dev);
+    p.signal_ptrs = reinterpret_cast<uint32_t* const*>(signal_ptrs_dev);
+    p.offset = elem_offset; p.elems = elems; p.epoch = epoch; p.pad_offset_words = signal_offset_bytes / 4;
+    p.rank = 0; p.world = world;
+    p.status = status_ptr();
+    if (p.status == nullptr) return cudaErrorInvalidDevice;
+    void* args[2] = {&p, &ctas_per_rank};
+    const void* fn = partial_is_bf16 ? reinterpret_cast<const void*>(ar::allreduce_one_device_kernel<true>)
+                                     : reinterpret_cast<const void*>(ar::allreduce_one_device_kernel<false>);
+    // cooperative: refused with cudaErrorCooperativeLaunchTooLarge when the CTAs cannot all be resident
+    return cudaLaunchCooperativeKernel(fn, dim3(world * ctas_per_rank), dim3(128), args, 0, static_cast<cudaStream_t>(stream));
 }
 
 int b200q_allreduce_set_unroll(int unroll)

@@ -24,13 +24,13 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
 // wrap-around).  On a timeout records (site, block) in *status and returns false.
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* status, uint32_t site)
 {
-    unsigned long long t0 = 0;            // the timer is read only every 64 failed polls
+    unsigned long long t0 = 0, limit = 0;            // the timer is read only every 64 failed polls
     uint32_t spins = 0;
     while (static_cast<int32_t>(ld_acquire_sys(flag) - epoch) < 0) {
         if ((++spins & 0x3Fu) == 0) {
             const unsigned long long now = ptx::globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > ptx::kWaitLimitNs) {
+            if (t0 == 0) { t0 = now; limit = ptx::peer_wait_limit_ns(status); }
+            else if (now - t0 > limit) {
                 atomicCAS(status, 0u, ptx::kStatusTimeout | (site << 24) | (blockIdx.x & 0xFFFFFFu));
                 return false;
             }

@@ -1,11 +1,18 @@
 // Status word, tensor-map encoding and device queries shared by all operators.
 #include "common.cuh"
+#include "ptx.cuh"
+#include "../../include/b200q.h"
 
 #include <mutex>
 
 namespace b200q {
 
-__device__ uint32_t g_status_word = 0;
+// word 0: status; words 2-3 / 4-5: wait limits in ns (inside one GPU / across ranks), see ptx.cuh
+__device__ __align__(16) uint32_t g_status_block[ptx::kStatusBlockWords] = {
+    0u, 0u,
+    static_cast<uint32_t>(ptx::kDefaultLocalWaitNs & 0xFFFFFFFFull), static_cast<uint32_t>(ptx::kDefaultLocalWaitNs >> 32),
+    static_cast<uint32_t>(ptx::kDefaultPeerWaitNs & 0xFFFFFFFFull), static_cast<uint32_t>(ptx::kDefaultPeerWaitNs >> 32),
+    0u, 0u};
 
 namespace {
 constexpr int kMaxDevices = 64;
@@ -26,7 +33,7 @@ uint32_t* status_ptr()
     std::lock_guard<std::mutex> lock(g_mu);
     if (g_status_addr[dev] == nullptr) {
         void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_block) != cudaSuccess) return nullptr;
         g_status_addr[dev] = static_cast<uint32_t*>(p);
     }
     return g_status_addr[dev];
@@ -78,3 +85,25 @@ bool make_tmap_2d_u8(CUtensorMap* map, const void* gaddr, uint64_t rows, uint64_
 }
 
 }  // namespace b200q
+
+extern "C" int b200q_status(unsigned int* host_out, int clear)
+{
+    using namespace b200q;
+    if (host_out == nullptr) return cudaErrorInvalidValue;
+    uint32_t* p = status_ptr();
+    if (p == nullptr) return cudaErrorInvalidDevice;
+    cudaError_t e = cudaMemcpy(host_out, p, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    if (clear) e = cudaMemset(p, 0, sizeof(uint32_t));
+    return e;
+}
+
+extern "C" int b200q_set_wait_limit_ms(int kind, int ms)
+{
+    using namespace b200q;
+    if ((kind != 0 && kind != 1) || ms < 1 || ms > 600000) return cudaErrorInvalidValue;
+    uint32_t* p = status_ptr();
+    if (p == nullptr) return cudaErrorInvalidDevice;
+    const unsigned long long ns = static_cast<unsigned long long>(ms) * 1000000ull;
+    return cudaMemcpy(p + (kind == 0 ? 2 : 4), &ns, sizeof(ns), cudaMemcpyHostToDevice);
+}

@@ -254,6 +254,59 @@ int b200q_gemm_fp8_rowcol_allreduce(const void* A, const void* B, void* partial_
                             nullptr, nullptr, N, &ar, static_cast<cudaStream_t>(stream));
 }
 
+int b200q_gemm_fp8_rowcol_allreduce_one_device(const void* const* A_host, const void* const* B_host,
+                                               const float* const* row_scale_host, const float* col_scale,
+                                               void* const* partial_host, void* const* counters_host,
+                                               const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                               void* const* flag_ptrs_dev, int M, int N, int K, int partial_is_bf16,
+                                               unsigned int flag_offset_bytes, unsigned int epoch, int world,
+                                               int ctas_per_rank, void* stream)
+{
+    using namespace b200q;
+    using namespace b200q::fp8;
+    if (A_host == nullptr || B_host == nullptr || row_scale_host == nullptr || col_scale == nullptr || partial_host == nullptr ||
+        counters_host == nullptr || partial_ptrs_dev == nullptr || out_ptrs_dev == nullptr || flag_ptrs_dev == nullptr)
+        return cudaErrorInvalidValue;
+    if (world < 1 || world > kOneDeviceMaxWorld || ctas_per_rank < 1 || flag_offset_bytes % 4 != 0) return cudaErrorInvalidValue;
+    if (N % 8 != 0) return cudaErrorInvalidValue;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    OneDeviceArgs a{};
+    a.ctas_per_rank = ctas_per_rank;
+    for (int r = 0; r < world; ++r) {
+        if (bad_operands(A_host[r], B_host[r], partial_host[r], M, N, K) || !aligned16(partial_host[r]) ||
+            row_scale_host[r] == nullptr || counters_host[r] == nullptr)
+            return cudaErrorInvalidValue;
+        Params& p = a.p[r];
+        p.M = M; p.N = N; p.K = K; p.C = partial_host[r]; p.ldc = N; p.alpha = 1.0f;
+        p.row_scale = row_scale_host[r]; p.col_scale = col_scale; p.col_scale2 = nullptr;
+        p.tiles_m = (M + kBM - 1) / kBM;
+        p.tiles_n = (N + 255) / 256;
+        p.group = 4;
+        if ((p.tiles_m + p.group - 1) / p.group > kMaxGroups) return cudaErrorInvalidValue;
+        p.status = status_ptr();
+        if (p.status == nullptr) return cudaErrorInvalidDevice;
+        p.partial_ptrs = partial_ptrs_dev;
+        p.out_ptrs = reinterpret_cast<__nv_bfloat16* const*>(out_ptrs_dev);
+        p.flag_ptrs = reinterpret_cast<uint32_t* const*>(flag_ptrs_dev);
+        p.partial_mc = nullptr; p.out_mc = nullptr;
+        p.counters = static_cast<uint32_t*>(counters_host[r]);
+        p.flag_offset_words = flag_offset_bytes / 4; p.epoch = epoch; p.rank = r; p.world = world;
+        p.reducer_stride = 1;
+        cudaError_t e = cudaMemsetAsync(p.counters, 0, (kMaxGroups + 1) * sizeof(uint32_t), st);
+        if (e != cudaSuccess) return e;
+        if (!make_tmap_2d_u8(&a.tmA[r], A_host[r], M, K, K, kBM, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
+        if (!make_tmap_2d_u8(&a.tmB[r], B_host[r], N, K, K, 256, kBK, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
+    }
+    const void* fn = partial_is_bf16 ? reinterpret_cast<const void*>(gemm_fp8_allreduce_one_device_kernel<__nv_bfloat16>)
+                                     : reinterpret_cast<const void*>(gemm_fp8_allreduce_one_device_kernel<float>);
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<256>::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    void* args[1] = {&a};
+    // cooperative: refused (cudaErrorCooperativeLaunchTooLarge) unless every CTA of every "rank" can be resident at once
+    return cudaLaunchCooperativeKernel(fn, dim3(world * ctas_per_rank), dim3(kBaseThreads + kReducerThreads), args,
+                                       Cfg<256>::kSmemBytes, st);
+}
+
 size_t b200q_fused_allreduce_flag_bytes(void)
 {
     return static_cast<size_t>(b200q::fp8::kMaxGroups + 1) * b200q::fp8::kMaxWorld * sizeof(uint32_t);

@@ -141,10 +141,12 @@ __device__ __forceinline__ void reducer_barrier()
     asm volatile("bar.sync 1, %0;" ::"n"(kReducerThreads) : "memory");
 }
 
+// The work of persistent CTA `cta` of `nctas` (the kernels below pass the block index and the grid size or,
+// when several ranks are emulated inside one launch, the CTA's index within its rank).  The tensor maps
+// are kernel parameters (__grid_constant__), addressed through pointers.
 template <int EPI, typename OutT, int BN, bool AR>
-__global__ void __launch_bounds__(kBaseThreads + (AR ? kReducerThreads : 0), 1)
-gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const __grid_constant__ CUtensorMap tmB2, const Params p)
+__device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* tmA, const CUtensorMap* tmB, const CUtensorMap* tmB2,
+                                              const Params& p, const int cta, const int nctas)
 {
     using CF = Cfg<BN>;
     constexpr int kStages = CF::kStages;
@@ -187,23 +189,23 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (ptx::elect_one()) {
-            ptx::tma_prefetch_desc(&tmA);
-            ptx::tma_prefetch_desc(&tmB);
-            if (EPI == kEpiSwiGLU) ptx::tma_prefetch_desc(&tmB2);
+            ptx::tma_prefetch_desc(tmA);
+            ptx::tma_prefetch_desc(tmB);
+            if (EPI == kEpiSwiGLU) ptx::tma_prefetch_desc(tmB2);
             int stage = 0; uint32_t phase = 0; bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = cta; tile < num_tiles && ok; tile += nctas) {
                 int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
                 const int m0 = tm * kBM, n0 = tn * kOutCols;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, p.status, 1)) { ok = false; break; }
                     const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + CF::kABytes;
                     ptx::mbar_arrive_expect_tx(full_bar(stage), kStageBytes);
-                    ptx::tma_load_2d(sa, &tmA, full_bar(stage), kb * kBK, m0);
+                    ptx::tma_load_2d(sa, tmA, full_bar(stage), kb * kBK, m0);
                     if (EPI == kEpiSwiGLU) {
-                        ptx::tma_load_2d(sb, &tmB, full_bar(stage), kb * kBK, n0);
-                        ptx::tma_load_2d(sb + (BN / 2) * kBK, &tmB2, full_bar(stage), kb * kBK, n0);
+                        ptx::tma_load_2d(sb, tmB, full_bar(stage), kb * kBK, n0);
+                        ptx::tma_load_2d(sb + (BN / 2) * kBK, tmB2, full_bar(stage), kb * kBK, n0);
                     } else {
-                        ptx::tma_load_2d(sb, &tmB, full_bar(stage), kb * kBK, n0);
+                        ptx::tma_load_2d(sb, tmB, full_bar(stage), kb * kBK, n0);
                     }
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
@@ -216,7 +218,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             constexpr uint32_t idesc = ptx::umma_idesc(0 /*E4M3*/, 0 /*E4M3*/, kBM, BN);
             int stage = 0; uint32_t phase = 0; bool ok = true;
             int t = 0;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+            for (int tile = cta; tile < num_tiles && ok; tile += nctas, ++t) {
                 const int buf = t & 1;
                 if (!ptx::mbar_wait(tempty_bar(buf), ((t >> 1) & 1u) ^ 1u, p.status, 2)) { ok = false; break; }
                 ptx::tcgen05_fence_after_sync();
@@ -242,7 +244,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         OutT* Cbase = static_cast<OutT*>(p.C);
         const bool ld_ok = ((p.ldc * (long long)sizeof(OutT)) % 16 == 0) && aligned16(p.C);
         int t = 0; bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
+        for (int tile = cta; tile < num_tiles && ok; tile += nctas, ++t) {
             const int buf = t & 1;
             int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
             const int row = tm * kBM + q * 32 + lane;
@@ -325,10 +327,10 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             // switch is microseconds, so throughput comes from the number of loads outstanding
             constexpr int kUnroll = 8;
             const int rstride = p.reducer_stride;
-            const long long nred = (gridDim.x + rstride - 1) / rstride;       // CTAs that take part
+            const long long nred = (nctas + rstride - 1) / rstride;       // CTAs that take part
             const long long stride = nred * kReducerThreads;
-            if (blockIdx.x % rstride != 0) continue;
-            for (long long vb = v0 + (blockIdx.x / rstride) * static_cast<long long>(kReducerThreads) + rt; vb < v1;
+            if (cta % rstride != 0) continue;
+            for (long long vb = v0 + (cta / rstride) * static_cast<long long>(kReducerThreads) + rt; vb < v1;
                  vb += stride * kUnroll) {
                 uint4 o[kUnroll];
                 long long e[kUnroll];
@@ -351,7 +353,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (ok) {
             if (rt == 0) {
                 __threadfence_system();
-                if (atomicAdd(p.counters + kMaxGroups, 1u) + 1u == gridDim.x)
+                if (atomicAdd(p.counters + kMaxGroups, 1u) + 1u == static_cast<uint32_t>(nctas))
                     for (int r = 0; r < p.world; ++r)
                         arc::st_release_sys(p.flag_ptrs[r] + p.flag_offset_words + kMaxGroups * kMaxWorld + p.rank, p.epoch);
             }
@@ -365,6 +367,35 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         ptx::tcgen05_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
+}
+
+template <int EPI, typename OutT, int BN, bool AR>
+__global__ void __launch_bounds__(kBaseThreads + (AR ? kReducerThreads : 0), 1)
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const __grid_constant__ CUtensorMap tmB2, const Params p)
+{
+    gemm_fp8_body<EPI, OutT, BN, AR>(&tmA, &tmB, &tmB2, p, blockIdx.x, gridDim.x);
+}
+
+// The down projection with the fused all-reduce for every rank of a small world inside ONE launch on ONE
+// device: CTAs [r * ctas_per_rank, (r + 1) * ctas_per_rank) play rank r on that rank's operands and buffers
+// (all in this device's memory).  Launched cooperatively, so the CTAs of all "ranks" are resident together
+// and the flags they raise for one another are seen; separate launches that wait on one another on one
+// device would have no such guarantee.  Peer loads/stores only.
+constexpr int kOneDeviceMaxWorld = 4;
+struct OneDeviceArgs {
+    alignas(64) CUtensorMap tmA[kOneDeviceMaxWorld];
+    alignas(64) CUtensorMap tmB[kOneDeviceMaxWorld];
+    Params p[kOneDeviceMaxWorld];
+    int ctas_per_rank;
+};
+template <typename OutT>
+__global__ void __launch_bounds__(kBaseThreads + kReducerThreads, 1)
+gemm_fp8_allreduce_one_device_kernel(const __grid_constant__ OneDeviceArgs a)
+{
+    const int r = blockIdx.x / a.ctas_per_rank;
+    gemm_fp8_body<kEpiRowCol, OutT, 256, true>(&a.tmA[r], &a.tmB[r], &a.tmB[r], a.p[r], blockIdx.x % a.ctas_per_rank,
+                                               a.ctas_per_rank);
 }
 
 }  // namespace fp8

@@ -15,7 +15,23 @@ namespace ptx {
 // Status word layout written on a timed-out wait: bit 31 set, bits [30:24] = site
 // id, bits [23:0] = block index (saturated).
 constexpr uint32_t kStatusTimeout = 0x80000000u;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s
+// The status word is the first of a small per-device block (defined in common.cu):
+//   word 0      status
+//   words 2-3   limit, in ns, of waits on something inside this GPU (mbarriers)      default 2 s
+//   words 4-5   limit, in ns, of waits on a flag that ANOTHER rank raises            default 10 s
+// The limits are settable from the host (b200q_set_wait_limit_ms); kernels read them through the
+// status pointer they already carry, and only on the slow path of a wait.
+constexpr unsigned long long kDefaultLocalWaitNs = 2000000000ull;
+constexpr unsigned long long kDefaultPeerWaitNs = 10000000000ull;
+constexpr int kStatusBlockWords = 8;
+__device__ __forceinline__ unsigned long long local_wait_limit_ns(const uint32_t* status)
+{
+    return *reinterpret_cast<const volatile unsigned long long*>(status + 2);
+}
+__device__ __forceinline__ unsigned long long peer_wait_limit_ns(const uint32_t* status)
+{
+    return *reinterpret_cast<const volatile unsigned long long*>(status + 4);
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p)
 {
@@ -95,7 +111,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 
-// Bounded wait on a phase parity.  Returns false after kWaitLimitNs, having recorded
+// Bounded wait on a phase parity.  Returns false after the local wait limit, having recorded
 // (site, block) in *status.  The caller must then leave its loop and fall through to
 // the kernel's tear-down.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t* status, uint32_t site)
@@ -103,13 +119,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
     if (mbar_try_wait(bar, parity)) return true;
     // The clock is read only every 256 failed polls (a poll itself blocks for a while in hardware), so a
     // wait that ends soon never pays for reading the global timer.
-    unsigned long long t0 = 0;
+    unsigned long long t0 = 0, limit = 0;
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0xFFu) == 0) {
             const unsigned long long now = globaltimer_ns();
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) {
+            if (t0 == 0) { t0 = now; limit = local_wait_limit_ns(status); }
+            else if (now - t0 > limit) {
                 uint32_t b = blockIdx.x > 0xFFFFFFu ? 0xFFFFFFu : blockIdx.x;
                 atomicCAS(status, 0u, kStatusTimeout | (site << 24) | b);
                 return false;

@@ -63,7 +63,8 @@ quant_rows_e4m3_kernel(const __nv_bfloat16* __restrict__ X, uint8_t* __restrict_
         if (threadIdx.x == 0) {
             float m = 0.0f;
             for (int i = 0; i < kThreads / 32; ++i) m = fmaxf(m, wmax[i]);
-            const float sc = m > 0.0f ? __fdiv_rn(m, 448.0f) : 1.0f;
+            // floor at the smallest normal float: the reciprocal below stays finite for rows of subnormal magnitudes
+            const float sc = m > 0.0f ? fmaxf(__fdiv_rn(m, 448.0f), 1.17549435e-38f) : 1.0f;
             s_scale = sc;
             S[row] = sc;
         }
@@ -109,16 +110,4 @@ extern "C" int b200q_quant_rows_e4m3(const void* X, void* Q, float* S, int rows,
     else if (vecs <= 256 * 8) quant::quant_rows_e4m3_kernel<256, 8, 3><<<grid, 256, 0, st>>>(x, q, S, rows, cols);
     else quant::quant_rows_e4m3_kernel<256, 14, 2><<<grid, 256, 0, st>>>(x, q, S, rows, cols);
     return cudaGetLastError();
-}
-
-extern "C" int b200q_status(unsigned int* host_out, int clear)
-{
-    using namespace b200q;
-    if (host_out == nullptr) return cudaErrorInvalidValue;
-    uint32_t* p = status_ptr();
-    if (p == nullptr) return cudaErrorInvalidDevice;
-    cudaError_t e = cudaMemcpy(host_out, p, sizeof(uint32_t), cudaMemcpyDeviceToHost);
-    if (e != cudaSuccess) return e;
-    if (clear) e = cudaMemset(p, 0, sizeof(uint32_t));
-    return e;
 }

@@ -23,8 +23,15 @@ Per rank and forward pass:
      it runs on the side stream under the NEXT forward's GEMMs (independent batches), partials and
      outputs double-buffered; the caller orders its use of Y after ``output_ready`` (an event) or
      calls ``wait()``.  Throughput mode for a stream of batches; "fused" is the latency mode.
+
+Every cross-rank wait inside the kernels is bounded (b200q_set_wait_limit_ms, 10 s by default).  A
+kernel that gives up returns early and leaves an UNDEFINED result; nothing in forward() can see
+that without synchronising, so callers that need the guarantee call ``check()`` (it synchronises
+and raises ``cudaop_b200.WaitTimeout``) before they trust Y — once per step, or per batch of steps.
 """
 from __future__ import annotations
+
+import warnings
 
 import torch
 
@@ -101,9 +108,11 @@ class TensorParallelMLP:
                     self._nbuf = 2 if comm == "pipelined" else 1
                     self._init_symmetric(T, H)
                     self.comm = comm if comm in ("symm", "pipelined") else "fused"
-                except Exception:
+                except Exception as exc:
                     if comm != "auto":
                         raise
+                    warnings.warn(f"symmetric memory is not available ({type(exc).__name__}: {exc}); "
+                                  "the all-reduce falls back to NCCL on fp32 partials")
                     self.comm = "nccl"
             if self.comm in ("fused", "pipelined"):
                 self.chunks = 1
@@ -111,7 +120,10 @@ class TensorParallelMLP:
             self._ar_done = [None, None]
             self.output_ready = None
             if self.comm == "nccl":
-                self.partial = torch.empty((T, H), dtype=self.partial_dtype, device=dev)
+                # NCCL rounds after every hop of its ring when it sums bf16, so this mode always moves fp32
+                # partials: fp32 accumulation and one rounding, as in the other modes
+                self.partial_dtype = torch.float32
+                self.partial = torch.empty((T, H), dtype=torch.float32, device=dev)
         self.kernel_launches_per_forward = 0
         self.top_kernel_events = None     # set to a list to collect (start, end) events of the gate/up kernel
         self.stage_events = None          # set to a list to collect 5 events bracketing the 4 kernels of a stage
@@ -281,8 +293,16 @@ class TensorParallelMLP:
         return self._y_all[b][:T]
 
     def wait(self):
-        """Makes the current stream wait for every all-reduce issued so far."""
+        """Makes the current stream wait for every all-reduce issued so far (no host synchronisation)."""
         if self.comm_stream is not None:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    def check(self):
+        """Synchronises this rank's device and raises cudaop_b200.WaitTimeout if any kernel issued so far
+        gave up on a bounded wait (a peer that never arrived): the outputs since the last check are then
+        undefined.  Clears the status word."""
+        self.wait()
+        with torch.cuda.device(self.device):
+            ops.check_status("TensorParallelMLP")
 
     __call__ = forward

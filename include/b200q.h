@@ -73,7 +73,10 @@ size_t b200q_gemm_nvfp4_workspace_bytes(int M, int N, int K);
  * the library, kept until exit), so the call performs no allocation of any kind.  Problems whose
  * b200q_gemm_nvfp4_workspace_bytes(M,N,K) exceeds b200q_gemm_nvfp4_static_max_bytes() are refused
  * with cudaErrorInvalidValue and a message on stderr (M = N = K = 8192 just fits).  The first call
- * on a device looks up the array's device address: issue it before any stream capture.  All calls
+ * on a device looks up the array's device address, and, like the first launch of any kernel, makes the
+ * driver load the kernels' images and set their attributes, which takes some device memory once: issue
+ * one warm-up call per device before any stream capture AND before the host hands the rest of the GPU's
+ * memory to its own pool.  From then on a call leaves the amount of free device memory untouched.  All calls
  * on a device share the one array — calls that may overlap on the GPU (several streams) race on
  * it; calls on one stream are safe, and no state has to be cleared between calls. */
 int b200q_gemm_nvfp4_static(const void* Aq, const void* SFA, const void* Bq, const void* SFB, void* C,
@@ -97,8 +100,10 @@ size_t b200q_nvfp4_sf_bytes(int rows, int K);      /* size of one blocked scale 
 int b200q_gemm_sp24_fp8(const void* Acomp, const void* Ameta, const void* B, void* C, int M, int N, int K,
                         float scale_a, float scale_b, void* stream);
 
-/* Tuning knobs (process-wide): width of the B tile, 128 / 192 / 256 columns. */
-int b200q_fp8_set_tile_n(int bn);      /* 0 = chosen per problem (default), 224 or 256 */
+/* Tuning knobs.  Every b200q_*_set_* function changes a PROCESS-WIDE setting read by later calls on any
+ * device; they are not synchronised with calls in flight on other host threads — set them once at
+ * start-up, before the threads that issue work are started.  All of them default to the measured best. */
+int b200q_fp8_set_tile_n(int bn);      /* width of the B tile: 0 = chosen per problem (default), 224 or 256 columns */
 /* SM partitioning for overlapping the stand-alone all-reduce with GEMMs: the persistent FP8 grids use at
  * most `sms` SMs (0 = all), and the all-reduce kernel asks for `bytes` of shared memory it does not use, so its
  * CTAs cannot share an SM with a GEMM CTA and land on the SMs left free. */
@@ -122,7 +127,7 @@ int b200q_sp24_set_tile_n(int bn);
 int b200q_sp24_set_2cta(int on);       /* 2:4-sparse GEMM on CTA pairs (256 x 224 tiles) when M > 128; default on */
 
 /* Activation quantiser: X[rows,cols] bf16 -> Q[rows,cols] E4M3 and S[rows] fp32,
- * S[r] = max|X[r,:]| / 448 (1 for a zero row), Q = rn_satfinite(X * (1 / S[r])).  No counterpart in
+ * S[r] = max(max|X[r,:]| / 448, 2^-126) (1 for a zero row), Q = rn_satfinite(X * (1 / S[r])).  No counterpart in
  * the reference (its MLP is fp32); needed on either side of the FP8 GEMMs.  cols % 8 == 0. */
 int b200q_quant_rows_e4m3(const void* X, void* Q, float* S, int rows, int cols, void* stream);
 
@@ -160,9 +165,39 @@ int b200q_gemm_fp8_rowcol_allreduce(const void* A, const void* B, void* partial_
 size_t b200q_fused_allreduce_flag_bytes(void);
 size_t b200q_fused_allreduce_counter_bytes(void);
 
+/* All ranks of a small world inside ONE cooperative launch on ONE device, for exercising the flag protocol
+ * and the reducers where only one GPU is at hand (tests): CTAs [r * ctas_per_rank, (r + 1) * ctas_per_rank)
+ * act as rank r.  The pointer tables are device arrays as above, every buffer in this device's memory; plain
+ * loads/stores only (no multicast).  Fails with cudaErrorCooperativeLaunchTooLarge instead of waiting when
+ * the CTAs of all ranks cannot be resident together.  Same arithmetic as the per-rank entry points
+ * (op/nccl/nccl_mlp_test.cu:181-195: fp32 sum in rank order, replicas identical). */
+int b200q_allreduce_to_bf16_one_device(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                       void* const* signal_ptrs_dev, int partial_is_bf16, long long elem_offset,
+                                       long long elems, int world, unsigned int epoch, unsigned int signal_offset_bytes,
+                                       int ctas_per_rank, void* stream);
+/* The same for b200q_gemm_fp8_rowcol_allreduce (world <= 4).  A_host / B_host / row_scale_host / partial_host /
+ * counters_host are HOST arrays of `world` device pointers (rank r's operands, its partial buffer = entry r of
+ * partial_ptrs_dev, its counter block); col_scale is shared; the three *_dev tables are device arrays. */
+int b200q_gemm_fp8_rowcol_allreduce_one_device(const void* const* A_host, const void* const* B_host,
+                                               const float* const* row_scale_host, const float* col_scale,
+                                               void* const* partial_host, void* const* counters_host,
+                                               const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                               void* const* flag_ptrs_dev, int M, int N, int K, int partial_is_bf16,
+                                               unsigned int flag_offset_bytes, unsigned int epoch, int world,
+                                               int ctas_per_rank, void* stream);
+
 /* Reads (and optionally clears) the device status word of the current device into *host_out.
- * 0 = no kernel of this library gave up on a bounded wait.  Synchronises the device. */
+ * 0 = no kernel of this library gave up on a bounded wait.  Otherwise bit 31 is set, bits [30:24] name the
+ * wait that ran out (1-7, 21-28: an mbarrier inside a GEMM; 5, 6: a flag of the fused all-reduce; 16, 17:
+ * the start / end barrier of the stand-alone all-reduce) and bits [23:0] the CTA.  A kernel that gave up
+ * returns early: ITS OUTPUT IS UNDEFINED (stale or partly written) and must not be used.  Synchronises the
+ * device. */
 int b200q_status(unsigned int* host_out, int clear);
+/* Limit of the bounded waits on the current device, in milliseconds (1 .. 600000).  kind 0: waits on
+ * something inside the GPU (mbarriers; default 2000); kind 1: waits on a flag that another rank raises
+ * (the all-reduce barriers and the fused reducers; default 10000 — ranks may legitimately be seconds apart
+ * on a first call or after a host stall, and a rank that gives up leaves an undefined result).  Synchronous. */
+int b200q_set_wait_limit_ms(int kind, int ms);
 
 #ifdef __cplusplus
 }

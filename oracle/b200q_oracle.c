@@ -301,8 +301,9 @@ void oracle_encode_f16_n(const float* in, uint16_t* out, size_t n)
     for (size_t i = 0; i < n; ++i) out[i] = oracle_encode_f16(in[i]);
 }
 
-/* Per-row (per-token) E4M3 quantisation: s[r] = max|x[r,:]| / 448 (1.0 for an
- * all-zero row), q = e4m3_rn(x * (1 / s[r])): one fp32 reciprocal per row, one fp32
+/* Per-row (per-token) E4M3 quantisation: s[r] = max(max|x[r,:]| / 448, 2^-126) (1.0 for
+ * an all-zero row; the floor keeps 1 / s finite for rows of subnormal magnitudes, which
+ * would otherwise turn their zeros into NaN), q = e4m3_rn(x * (1 / s[r])): one fp32 reciprocal per row, one fp32
  * product per element (both round-to-nearest), then the E4M3 rounding.  No reference
  * counterpart; the rule is stated here and the kernel reproduces it bit for bit. */
 void oracle_quant_rows_e4m3(const float* x, uint8_t* q, float* s, int rows, int cols)
@@ -311,7 +312,7 @@ void oracle_quant_rows_e4m3(const float* x, uint8_t* q, float* s, int rows, int 
         const float* xr = x + (size_t)r * cols;
         float mx = 0.0f;
         for (int c = 0; c < cols; ++c) mx = fmaxf(mx, fabsf(xr[c]));
-        float sc = mx > 0.0f ? mx / 448.0f : 1.0f;
+        float sc = mx > 0.0f ? fmaxf(mx / 448.0f, 1.17549435e-38f) : 1.0f;
         volatile float inv = 1.0f / sc;       /* volatile: keep the two roundings separate */
         s[r] = sc;
         for (int c = 0; c < cols; ++c) {

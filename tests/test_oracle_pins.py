@@ -225,6 +225,15 @@ def test_quantisers_round_trip_and_scale_rules():
     assert np.all(nib.reshape(5, 4, 16).max(-1) >= 5)
 
 
+def test_row_quantiser_scale_floor_keeps_tiny_rows_finite():
+    x = np.zeros((3, 16), np.float32)
+    x[0, 0] = 1e-37; x[1, 1] = 9.2e-41; x[2, 2] = 1e-35
+    q, s = oracle.quant_rows_e4m3(x)
+    assert s[0] == np.float32(2.0 ** -126) and s[1] == np.float32(2.0 ** -126) and s[2] > np.float32(2.0 ** -126)
+    assert ((q & 0x7F) != 0x7F).all() and np.isfinite(oracle.decode_e4m3(q)).all()
+    assert (q[:, 8:] == 0).all()                               # zeros stay zeros
+
+
 def test_w4a16_dequant_rule():
     xb, wq, s = oracle.make_w4a16_case(1, 4, 256, group=128, seed=0)
     W = oracle.dequant_w4(wq, s, 128)

@@ -102,3 +102,27 @@ def test_activation_quantiser_is_bit_exact(shape):
     qn = q.cpu().numpy()
     same = (qn == q_ref) | (((qn & 0x7F) == 0) & ((q_ref & 0x7F) == 0))     # +0 / -0
     assert same.all()
+
+
+def test_activation_quantiser_rows_of_tiny_and_subnormal_values_stay_finite():
+    """A row whose largest magnitude is tiny (below about 5.3e-36) would give a scale under 2^-126 and a reciprocal
+    of +inf, turning the row's zeros into NaN bytes (0x7F) that poison the next GEMM: the scale is
+    floored at 2^-126 instead (kernel and oracle alike)."""
+    import cudaop_b200 as ops
+    rows, cols = 6, 256
+    x = np.zeros((rows, cols), np.float32)
+    x[0, ::3] = 1e-37; x[0, 1::3] = -3e-38                     # below the threshold, zeros in between
+    x[1, 5] = 9.2e-41                                          # the smallest bf16 subnormal alone
+    x[2, :] = 1e-39; x[2, 7] = 0.0
+    x[3, ::2] = 1e-35                                          # just above the threshold
+    x[4, 3] = 1.0; x[4, 4] = 1e-40                             # an ordinary row with a subnormal element
+    xb = oracle.encode_bf16(x)
+    q, s = ops.quant_rows_e4m3(dev(xb, torch.bfloat16))
+    torch.cuda.synchronize()
+    qn, sn = q.cpu().numpy(), s.cpu().numpy()
+    assert np.isfinite(sn).all() and (sn > 0).all()
+    assert ((qn & 0x7F) != 0x7F).all()                         # no NaN byte anywhere
+    q_ref, s_ref = oracle.quant_rows_e4m3(oracle.decode_bf16(xb))
+    assert np.array_equal(sn.view(np.uint32), s_ref.view(np.uint32))
+    assert ((qn == q_ref) | (((qn | q_ref) & 0x7F) == 0)).all()
+    assert (qn[5] == 0).all() and sn[5] == 1.0                 # all-zero row: scale 1

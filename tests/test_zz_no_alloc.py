@@ -50,6 +50,31 @@ def test_static_entry_matches_the_workspace_entry_on_two_calls_in_a_row():
     assert rep["rel_fro"] <= 1e-3 and rep["max_ulp_floor"] <= 2.0, rep
 
 
+def test_static_entry_takes_no_device_memory_once_warm():
+    """After one warm-up call (which loads the kernels' images and looks up the array's address) further
+    calls leave the driver's count of free device memory exactly where it was."""
+    import cudaop_b200 as ops
+    L = ops.lib()
+    M, N, K = 256, 384, 512
+    aq, sfa, ga, bq, sfb, gb = oracle.make_nvfp4_case(M, N, K, seed=43)
+    a, sa, b, sb = dev(aq), dev(sfa), dev(bq), dev(sfb)
+    out = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        assert L.b200q_gemm_nvfp4_static(a.data_ptr(), sa.data_ptr(), b.data_ptr(), sb.data_ptr(), out.data_ptr(),
+                                         M, N, K, ga, gb, st) == 0
+    call()                                      # warm-up: module load, function attributes, symbol address
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        call()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+    assert ops.status() == 0
+
+
 def test_static_entry_refuses_problems_beyond_its_array():
     import cudaop_b200 as ops
     L = ops.lib()
