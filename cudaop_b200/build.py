@@ -1,8 +1,12 @@
 """Builds libb200q.so (the C-ABI library) and the per-operator benchmark executables
 in-tree with nvcc for sm_100a.  No GPU is needed to build.
 
-    python -m cudaop_b200.build            # library + executables
+    python -m cudaop_b200.build            # library + torch extension + executables
     python -m cudaop_b200.build --lib      # library only
+
+The torch extension cudaop_b200._C is built by the repository's setup.py (CUDAExtension, ninja) with
+TORCH_CUDA_ARCH_LIST=10.0a and import-checked afterwards, as the reference's build scripts do
+(op/grouped_gemm/build.py:15-53, op/lora_moe/build.py:53-67).
 """
 from __future__ import annotations
 
@@ -74,10 +78,36 @@ def build_bench(force: bool = False) -> list[str]:
     return outs
 
 
+def build_ext(force: bool = False) -> str:
+    """cudaop_b200/_C*.so via setup.py build_ext --inplace; then checks that the module imports and exports
+    every operator."""
+    import glob
+    src = os.path.join(HERE, "csrc_ext", "ops.cpp")
+    deps = [src, LIB, os.path.join(ROOT, "include", "b200q.h"), os.path.join(ROOT, "setup.py")]
+    found = glob.glob(os.path.join(HERE, "_C*.so"))
+    if force or not found or _newer(found[0], deps):
+        env = dict(os.environ, TORCH_CUDA_ARCH_LIST="10.0a", MAX_JOBS=os.environ.get("MAX_JOBS", "8"))
+        r = subprocess.run([sys.executable, "setup.py", "build_ext", "--inplace"], cwd=ROOT, env=env,
+                           stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout)
+            raise RuntimeError("building cudaop_b200._C failed")
+        found = glob.glob(os.path.join(HERE, "_C*.so"))
+    if ROOT not in sys.path:
+        sys.path.insert(0, ROOT)
+    import importlib
+    ops = importlib.import_module("cudaop_b200")
+    missing = [n for n in ops.EXTENSION_OPS if not callable(getattr(ops._C, n, None))]
+    if missing:
+        raise RuntimeError(f"cudaop_b200._C does not export {missing}")
+    return found[0]
+
+
 def main() -> None:
     force = "--force" in sys.argv
     print(build_lib(force))
     if "--lib" not in sys.argv:
+        print(build_ext(force))
         for e in build_bench(force):
             print(e)
 

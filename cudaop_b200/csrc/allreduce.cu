@@ -103,6 +103,12 @@ allreduce_one_device_kernel(Params p, int ctas_per_rank)
     allreduce_body<false, PartialBf16, 2>(p, blockIdx.x % ctas_per_rank, ctas_per_rank);
 }
 
+// One tiny CTA: a barrier over all ranks on the launching streams (bounded like every other wait).
+__global__ void __launch_bounds__(32) rank_barrier_kernel(const Params p)
+{
+    rank_barrier(p, 0, 0);
+}
+
 int g_unroll = 4;
 int g_threads = 256;
 int g_reserved_smem = 0;   // dynamic shared memory requested only to keep the CTAs off SMs that host a GEMM CTA
@@ -178,6 +184,24 @@ int b200q_allreduce_to_bf16_one_device(const void* const* partial_ptrs_dev, void
                                      : reinterpret_cast<const void*>(ar::allreduce_one_device_kernel<false>);
     // cooperative: refused with cudaErrorCooperativeLaunchTooLarge when the CTAs cannot all be resident
     return cudaLaunchCooperativeKernel(fn, dim3(world * ctas_per_rank), dim3(128), args, 0, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200q_rank_barrier_signal_bytes(void) { return static_cast<size_t>(b200q::ar::kMaxWorld) * sizeof(uint32_t); }
+
+int b200q_rank_barrier(void* const* signal_ptrs_dev, int rank, int world, unsigned int epoch,
+                       unsigned int signal_offset_bytes, void* stream)
+{
+    using namespace b200q;
+    if (signal_ptrs_dev == nullptr || world < 1 || world > ar::kMaxWorld || rank < 0 || rank >= world ||
+        signal_offset_bytes % 4 != 0)
+        return cudaErrorInvalidValue;
+    ar::Params p{};
+    p.signal_ptrs = reinterpret_cast<uint32_t* const*>(signal_ptrs_dev);
+    p.epoch = epoch; p.pad_offset_words = signal_offset_bytes / 4; p.rank = rank; p.world = world;
+    p.status = status_ptr();
+    if (p.status == nullptr) return cudaErrorInvalidDevice;
+    ar::rank_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return cudaGetLastError();
 }
 
 int b200q_allreduce_set_unroll(int unroll)

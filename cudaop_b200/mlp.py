@@ -306,3 +306,87 @@ class TensorParallelMLP:
             ops.check_status("TensorParallelMLP")
 
     __call__ = forward
+
+
+class HostFedMLP:
+    """Feeds a TensorParallelMLP with batches that live in pinned HOST memory and leaves the results there.
+
+    The end-to-end path of a job whose activations arrive from the host: per step every rank copies its
+    1/R of X from pinned memory over its own PCIe link, the ranks complete each other's copy of X over
+    NVLink, the MLP runs, and every rank writes its 1/R of the (replicated) result back to pinned memory.
+    All copies run on their own streams and are double-buffered, so the input copy of step i+1 and the
+    output copy of step i-1 overlap the GEMMs of step i.
+
+    With R > 1 the X buffers are symmetric memory.  After its host-to-device copy each rank passes a
+    stream-ordered barrier (b200q_rank_barrier: every rank's slice has landed) and then pulls the other
+    ranks' slices with plain device-to-device copies (copy engines, no SM time taken from the GEMMs, no
+    TMA on peer memory).  The barrier of step i+1 is enqueued behind the pulls of step i, so a rank
+    overwrites a slice only after every peer has read it.
+    """
+
+    def __init__(self, mlp: TensorParallelMLP, tokens: int):
+        self.mlp, self.tokens = mlp, tokens
+        self.rank, self.world, dev = mlp.rank, mlp.world, mlp.device
+        H = mlp.hidden
+        if tokens % self.world != 0 or tokens > mlp.max_tokens:
+            raise ValueError("tokens must be divisible by the number of ranks and fit the MLP's buffers")
+        self.rows = tokens // self.world
+        self.lo, self.hi = self.rank * self.rows, (self.rank + 1) * self.rows
+        self.copy_in, self.copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        self._x_free = [None, None]     # event: the forward that last read X buffer b has been issued
+        self._step = 0
+        self._epoch = 0
+        if self.world == 1:
+            self.xbuf = [torch.empty((tokens, H), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+            return
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        group = mlp.group if mlp.group is not None else dist.group.WORLD
+        self._xsym = symm.empty((2, tokens, H), dtype=torch.bfloat16, device=dev)
+        self._flags = symm.empty((ops.lib().b200q_rank_barrier_signal_bytes() // 4,), dtype=torch.int32, device=dev)
+        self._flags.zero_()
+        self._hx = symm.rendezvous(self._xsym, group)
+        self._hf = symm.rendezvous(self._flags, group)
+        self.xbuf = [self._xsym[0], self._xsym[1]]
+        # peer r's copy of both X buffers, as tensors this rank can copy from
+        self._peer = [self._hx.get_buffer(r, (2, tokens, H), torch.bfloat16, 0) if r != self.rank else None
+                      for r in range(self.world)]
+        torch.cuda.synchronize(dev)
+        dist.barrier(group=group)
+
+    def step(self, x_host: torch.Tensor, y_host: torch.Tensor):
+        """Enqueues one forward pass: x_host / y_host are pinned [tokens, hidden] bf16 tensors; this rank
+        reads rows [lo, hi) of x_host and writes rows [lo, hi) of y_host.  Returns at once; finish()
+        orders the current stream after everything issued."""
+        mlp, b = self.mlp, self._step & 1
+        self._step += 1
+        main = torch.cuda.current_stream()
+        lo, hi, rows = self.lo, self.hi, self.rows
+        with torch.cuda.stream(self.copy_in):
+            if self._x_free[b] is not None:
+                self.copy_in.wait_event(self._x_free[b])
+            self.xbuf[b][lo:hi].copy_(x_host[lo:hi], non_blocking=True)
+            if self.world > 1:
+                self._epoch += 1
+                ops._raise(ops.lib().b200q_rank_barrier(self._hf.buffer_ptrs_dev, self.rank, self.world, self._epoch, 0,
+                                                        self.copy_in.cuda_stream), "b200q_rank_barrier")
+                for r in range(self.world):
+                    if r != self.rank:
+                        self.xbuf[b][r * rows:(r + 1) * rows].copy_(self._peer[r][b, r * rows:(r + 1) * rows], non_blocking=True)
+            ready = torch.cuda.Event(); ready.record(self.copy_in)
+        main.wait_event(ready)
+        y = mlp.forward(self.xbuf[b][:self.tokens])
+        done = torch.cuda.Event(); done.record(main)
+        self._x_free[b] = done
+        side = mlp.comm_stream if (self.world > 1 and mlp.comm == "pipelined") else self.copy_out
+        with torch.cuda.stream(side):                 # ordered after this step's GEMMs (and its all-reduce)
+            side.wait_event(done)
+            y_host[lo:hi].copy_(y[lo:hi], non_blocking=True)
+
+    def finish(self):
+        main = torch.cuda.current_stream()
+        main.wait_stream(self.copy_in); main.wait_stream(self.copy_out)
+        self.mlp.wait()
+
+    bytes_in_per_step = property(lambda self: self.tokens * self.mlp.hidden * 2)
+    bytes_out_per_step = property(lambda self: self.tokens * self.mlp.hidden * 2)

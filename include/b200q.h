@@ -148,6 +148,16 @@ int b200q_allreduce_set_unroll(int unroll);     /* tuning knob: independent redu
 int b200q_allreduce_set_threads(int threads);   /* tuning knob: threads per CTA of the all-reduce kernel, 128/256/512 */
 size_t b200q_allreduce_signal_bytes(void);
 
+/* A barrier over the ranks, in stream order: the kernel ends on this rank once every rank's call with the same
+ * `epoch` (growing by one per call) has started, i.e. once everything enqueued before it on every rank's
+ * launching stream has completed.  `signal_ptrs_dev`: device array of `world` pointers to every rank's flag words
+ * (peer-mapped, b200q_rank_barrier_signal_bytes() bytes from signal_offset_bytes on, zeroed once).  Bounded like
+ * every wait of the library (cross-rank limit; status site 16).  Used to order copies between ranks' buffers;
+ * it plays the part of the stream synchronisation around ncclAllReduce in op/nccl/nccl_mlp_test.cu:181-195. */
+int b200q_rank_barrier(void* const* signal_ptrs_dev, int rank, int world, unsigned int epoch,
+                       unsigned int signal_offset_bytes, void* stream);
+size_t b200q_rank_barrier_signal_bytes(void);
+
 /* The MLP's row-parallel down projection with the all-reduce fused into the same kernel (one
  * kernel in place of GEMM -> ncclAllReduce, op/nccl/nccl_mlp_test.cu:170-195): every rank calls it
  * at the same time; the kernel writes partial tiles (fp32, or bf16 with partial_is_bf16) to `partial_local` (this rank's entry of

@@ -42,3 +42,25 @@ def test_missing_library_is_a_loud_error(monkeypatch):
         assert False, "expected ImportError"
     except ImportError:
         pass
+
+
+def test_torch_extension_is_built_in_tree_and_exports_every_operator():
+    import __graft_entry__ as g
+    g.build()
+    import cudaop_b200 as ops
+    assert ops._C is not None, ops._C_ERROR
+    assert os.path.dirname(os.path.abspath(ops._C.__file__)) == os.path.join(ROOT, "cudaop_b200")
+    for n in ops.EXTENSION_OPS:
+        assert callable(getattr(ops._C, n)), n
+        assert callable(getattr(ops, n)), n
+
+
+def test_missing_extension_is_a_loud_error(monkeypatch):
+    import cudaop_b200 as ops
+    monkeypatch.setattr(ops, "_C", None)
+    monkeypatch.setattr(ops, "_C_ERROR", ImportError("not built"))
+    try:
+        ops.gemm_fp8(None, None, 1.0, 1.0)
+        assert False, "expected ImportError"
+    except ImportError:
+        pass

@@ -72,7 +72,12 @@ def test_two_rank_shards_sum_to_the_single_rank_result(pdt):
     acc = torch.zeros((T, H), dtype=torch.float32, device="cuda")
     hs, ref_sum = [], np.zeros((T, H), np.float32)
     for r in range(2):
+        # comm="nccl" only to get a rank object without a process group; that mode always keeps fp32 partials,
+        # so the bf16 case gives the rank a bf16 partial buffer by hand (what the symmetric-memory modes hold)
         m = TensorParallelMLP(*_tensors(case), rank=r, world=2, max_tokens=T, comm="nccl", partial_dtype=pdt)
+        assert m.partial_dtype == torch.float32
+        m.partial_dtype = pdt
+        m.partial = torch.empty((T, H), dtype=pdt, device="cuda")
         assert m.wg.shape == (I // 2, H) and m.wd.shape == (H, I // 2)
         m._stage(x, None, 0, T)
         torch.cuda.synchronize()
