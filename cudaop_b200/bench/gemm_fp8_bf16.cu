@@ -28,7 +28,7 @@ static bool run_case(const Case& c, const Args& a)
     std::vector<uint16_t> C((size_t)M * N);
     CK(cudaMemcpy(C.data(), dC, C.size() * 2, cudaMemcpyDeviceToHost));
     // sampled rows against the host reference on the dequantised operands
-    const std::vector<int> rows = sample_rows(M, (size_t)M * N * K <= (1ull << 31) ? M : 32, a.seed);
+    const std::vector<int> rows = sample_rows(M, (size_t)M * N * K <= (1ull << 31) ? M : 256, a.seed);
     std::vector<float> Ad(rows.size() * (size_t)K), Bd((size_t)N * K), ref(rows.size() * (size_t)N);
     for (size_t r = 0; r < rows.size(); ++r)
         for (int k = 0; k < K; ++k) Ad[r * K + k] = decode_e4m3(Aq[(size_t)rows[r] * K + k]) * sa;
@@ -40,7 +40,7 @@ static bool run_case(const Case& c, const Args& a)
     for (size_t r = 0; r < rows.size(); ++r) std::memcpy(&got[r * N], &C[(size_t)rows[r] * N], (size_t)N * 2);
     std::printf("[STAGE] reference: %zu of %d rows on %u host threads, %.2f s, %.2f GFLOP/s (reference CPU loop)\n",
                 rows.size(), M, std::thread::hardware_concurrency(), cpu_s, 2.0 * rows.size() * N * K / cpu_s / 1e9);
-    bool ok = report_errors(compare_bf16(got.data(), ref.data(), ref.size(), K));
+    bool ok = report_errors(compare_bf16(got.data(), ref.data(), ref.size(), K), "gemm_fp8_bf16", c.name);
     if (ok && !a.correctness_only) {
         Timing t = time_kernel(launch, st);
         const double tf = 2.0 * M * N * K / (t.median_ms * 1e-3) / 1e12;

@@ -38,7 +38,7 @@ static bool run_case(const Case& c, const Args& a)
                 c.name, M, N, K, (unsigned long long)a.seed);
     std::vector<float> A = normal((size_t)M * K, a.seed), B = normal((size_t)N * K, a.seed + 1), Bd;
     std::vector<uint8_t> Aq, Bq, sfa, sfb; float ga, gb;
-    const std::vector<int> rows = sample_rows(M, (size_t)M * N * K <= (1ull << 31) ? M : 32, a.seed);
+    const std::vector<int> rows = sample_rows(M, (size_t)M * N * K <= (1ull << 31) ? M : 256, a.seed);
     std::vector<float> Adq;
     quantise(A, M, K, Aq, sfa, ga, &Adq);
     quantise(B, N, K, Bq, sfb, gb, &Bd);
@@ -60,7 +60,7 @@ static bool run_case(const Case& c, const Args& a)
     for (size_t r = 0; r < rows.size(); ++r) std::memcpy(&got[r * N], &C[(size_t)rows[r] * N], (size_t)N * 2);
     std::printf("[STAGE] reference: %zu of %d rows on %u host threads, %.2f s, %.2f GFLOP/s (reference CPU loop)\n",
                 rows.size(), M, std::thread::hardware_concurrency(), cpu_s, 2.0 * rows.size() * N * K / cpu_s / 1e9);
-    bool ok = report_errors(compare_bf16(got.data(), ref.data(), ref.size(), K));
+    bool ok = report_errors(compare_bf16(got.data(), ref.data(), ref.size(), K), "gemm_nvfp4_bf16", c.name);
     if (ok && !a.correctness_only) {
         Timing t = time_kernel(launch, st);
         const double tf = 2.0 * M * N * K / (t.median_ms * 1e-3) / 1e12;

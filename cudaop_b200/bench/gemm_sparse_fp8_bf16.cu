@@ -39,7 +39,7 @@ static bool run_case(const Case& c, const Args& a)
     if (a.profile) { launch(0); launch(0); CK(cudaStreamSynchronize(st)); check_status(); std::printf("[SUCCESS] profile launch done\n"); return true; }
     launch(0); CK(cudaStreamSynchronize(st)); check_status();
     std::vector<uint16_t> C((size_t)M * N); CK(cudaMemcpy(C.data(), dC, C.size() * 2, cudaMemcpyDeviceToHost));
-    const std::vector<int> rows = sample_rows(M, (size_t)M * N * K <= (1ull << 31) ? M : 32, a.seed);
+    const std::vector<int> rows = sample_rows(M, (size_t)M * N * K <= (1ull << 31) ? M : 256, a.seed);
     std::vector<float> Ad(rows.size() * (size_t)K, 0.0f), Bd((size_t)N * K), ref(rows.size() * (size_t)N);
     for (size_t r = 0; r < rows.size(); ++r)
         for (int g = 0; g < K / 4; ++g) {
@@ -55,7 +55,7 @@ static bool run_case(const Case& c, const Args& a)
     for (size_t r = 0; r < rows.size(); ++r) std::memcpy(&got[r * N], &C[(size_t)rows[r] * N], (size_t)N * 2);
     std::printf("[STAGE] reference: %zu of %d rows (dense expanded A) on %u host threads, %.2f s, %.2f GFLOP/s\n",
                 rows.size(), M, std::thread::hardware_concurrency(), cpu_s, 2.0 * rows.size() * N * K / cpu_s / 1e9);
-    bool ok = report_errors(compare_bf16(got.data(), ref.data(), ref.size(), K));
+    bool ok = report_errors(compare_bf16(got.data(), ref.data(), ref.size(), K), "gemm_sparse_fp8_bf16", c.name);
     if (ok && !a.correctness_only) {
         Timing t = time_kernel(launch, st);
         const double tf = 2.0 * M * N * K / (t.median_ms * 1e-3) / 1e12;

@@ -46,7 +46,7 @@ static bool run_case(const Case& c, const Args& a)
     host_gemm_ref(Xf.data(), Wd.data(), ref.data(), M, N, K);
     const double cpu_s = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
     std::printf("[STAGE] reference: full problem on the host, %.3f s, %.2f GFLOP/s (reference CPU loop)\n", cpu_s, 2.0 * M * N * K / cpu_s / 1e9);
-    bool ok = report_errors(compare_bf16(Y.data(), ref.data(), ref.size(), K));
+    bool ok = report_errors(compare_bf16(Y.data(), ref.data(), ref.size(), K), "gemm_w4a16_bf16", c.name);
     if (ok && !a.correctness_only) {
         Timing t = time_kernel(launch, st);
         const double bytes = (double)N * K / 2 + (double)N * G * 2 + 2.0 * M * K + 2.0 * M * N;

@@ -6,9 +6,12 @@
 // (build_reference, :208-300), max-abs / max-rel comparison (:444-458), bit-exact replica check
 // (:646-664), warm-up + timed iterations with the slowest rank's time reported (:483-526).
 // Differences asked for by the benchmark configuration: SwiGLU, E4M3 weights with per-channel
-// scales, bf16 activations, --gpus {1,2,4,8}, one host thread per device, and --comm:
-//   fused  the library's down-projection kernel with the all-reduce fused in (peer loads/stores)
-//   nccl   b200q GEMMs + ncclAllReduce(bf16, sum) as in the reference
+// scales, bf16 activations, --gpus {1,2,4,8}, one host thread per device, and --comm (or B200Q_MLP_COMM):
+//   fused      the library's down-projection kernel with the all-reduce fused in (peer loads/stores)
+//   pipelined  the library's stand-alone all-reduce kernel on a side stream under the NEXT step's GEMMs,
+//              partials and outputs double-buffered (the throughput mode bench.py times; peer loads/stores
+//              here: the in-switch transport needs a multicast mapping, which only the Python layer sets up)
+//   nccl       b200q GEMMs + ncclAllReduce(bf16, sum) as in the reference
 #include <nccl.h>
 
 #include <atomic>
@@ -25,13 +28,16 @@ using namespace bench;
 
 struct Rank {
     int dev = 0;
-    cudaStream_t st{};
+    cudaStream_t st{}, cs{};                   // GEMM stream, all-reduce side stream (pipelined mode)
     uint8_t *wg{}, *wu{}, *wd{}, *xq{}, *hq{};
     float *sg{}, *su{}, *sd{}, *sx{}, *sh{};
     uint16_t *x{}, *h{}, *partial{}, *y{};
-    uint32_t *flags{}, *counters{};
+    uint16_t *partial2{}, *y2{};               // second buffers of the pipelined mode
+    uint32_t *flags{}, *counters{}, *signals{};
     void **partial_tab{}, **out_tab{}, **flag_tab{};
-    cudaEvent_t e0{}, e1{};
+    void **partial_tab2{}, **out_tab2{}, **signal_tab{};
+    cudaEvent_t e0{}, e1{}, gemm_done{}, ar_done[2]{};
+    bool ar_used[2] = {false, false};
 };
 
 static void run_threads(int n, const std::function<void(int)>& fn)
@@ -51,6 +57,8 @@ int main(int argc, char** argv)
     if (a.n > 0) hidden = a.n;
     if (a.k > 0) inter = a.k;
     if (const char* c = std::getenv("B200Q_MLP_COMM")) comm = c;
+    if (!a.comm.empty()) comm = a.comm;
+    if (comm != "fused" && comm != "pipelined" && comm != "nccl") { std::printf("[FAILED] --comm must be fused, pipelined or nccl\n"); return 1; }
     const int R = a.gpus;
     int ndev = 0; CK(cudaGetDeviceCount(&ndev));
     if (R < 1 || R > ndev || inter % R != 0) { std::printf("[FAILED] need %d GPUs (have %d) and intermediate %% gpus == 0\n", R, ndev); return 1; }
@@ -93,6 +101,11 @@ int main(int argc, char** argv)
         CK(cudaMalloc(&k.partial, (size_t)tokens * hidden * 2)); CK(cudaMalloc(&k.y, (size_t)tokens * hidden * 2));
         CK(cudaMalloc(&k.flags, b200q_fused_allreduce_flag_bytes())); CK(cudaMemset(k.flags, 0, b200q_fused_allreduce_flag_bytes()));
         CK(cudaMalloc(&k.counters, b200q_fused_allreduce_counter_bytes()));
+        CK(cudaStreamCreateWithFlags(&k.cs, cudaStreamNonBlocking));
+        CK(cudaEventCreateWithFlags(&k.gemm_done, cudaEventDisableTiming));
+        for (auto& e : k.ar_done) CK(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        CK(cudaMalloc(&k.partial2, (size_t)tokens * hidden * 2)); CK(cudaMalloc(&k.y2, (size_t)tokens * hidden * 2));
+        CK(cudaMalloc(&k.signals, b200q_allreduce_signal_bytes())); CK(cudaMemset(k.signals, 0, b200q_allreduce_signal_bytes()));
     };
     for (int r = 0; r < R; ++r) setup(rk[r], r, R);
     setup(rk[R], 0, 1);
@@ -102,6 +115,8 @@ int main(int argc, char** argv)
         for (int j = 0; j < R; ++j) { pt[j] = rk[j].partial; ot[j] = rk[j].y; ft[j] = rk[j].flags; }
         CK(cudaSetDevice(rk[r].dev));
         rk[r].partial_tab = to_device(pt); rk[r].out_tab = to_device(ot); rk[r].flag_tab = to_device(ft);
+        for (int j = 0; j < R; ++j) { pt[j] = rk[j].partial2; ot[j] = rk[j].y2; ft[j] = rk[j].signals; }
+        rk[r].partial_tab2 = to_device(pt); rk[r].out_tab2 = to_device(ot); rk[r].signal_tab = to_device(ft);
     }
     std::vector<ncclComm_t> comms(R);
     if (comm == "nccl" && R > 1) { std::vector<int> devs(R); for (int i = 0; i < R; ++i) devs[i] = i; CKN(ncclCommInitAll(comms.data(), R, devs.data())); }
@@ -116,7 +131,17 @@ int main(int argc, char** argv)
         else if (comm == "fused")
             CKQ(b200q_gemm_fp8_rowcol_allreduce(k.hq, k.wd, k.partial, tokens, hidden, l, k.sh, k.sd, k.partial_tab, k.out_tab,
                                                 k.flag_tab, nullptr, nullptr, 1, k.counters, 0, ep, rank, world, k.st));
-        else {
+        else if (comm == "pipelined") {
+            const int b = ep & 1;                                   // buffers alternate; the all-reduce of step i runs under step i + 1
+            if (k.ar_used[b]) CK(cudaStreamWaitEvent(k.st, k.ar_done[b], 0));   // the all-reduce that last read partial[b] / wrote y[b]
+            CKQ(b200q_gemm_fp8_rowcol(k.hq, k.wd, b ? k.partial2 : k.partial, tokens, hidden, l, k.sh, k.sd, 0, k.st));
+            CK(cudaEventRecord(k.gemm_done, k.st));
+            CK(cudaStreamWaitEvent(k.cs, k.gemm_done, 0));
+            CKQ(b200q_allreduce_to_bf16(b ? k.partial_tab2 : k.partial_tab, b ? k.out_tab2 : k.out_tab, k.signal_tab, nullptr, nullptr, 1,
+                                        0, (long long)tokens * hidden, rank, world, ep, 0, 148, k.cs));
+            CK(cudaEventRecord(k.ar_done[b], k.cs));
+            k.ar_used[b] = true;
+        } else {
             CKQ(b200q_gemm_fp8_rowcol(k.hq, k.wd, k.y, tokens, hidden, l, k.sh, k.sd, 0, k.st));
             CKN(ncclAllReduce(k.y, k.y, (size_t)tokens * hidden, ncclBfloat16, ncclSum, comms[rank], k.st));
         }
@@ -131,7 +156,9 @@ int main(int argc, char** argv)
             run_threads(R, [&](int r) { CK(cudaSetDevice(rk[r].dev)); forward(rk[r], r, R, ep); });
         }
     };
-    auto sync_all = [&]() { for (int r = 0; r < R; ++r) { CK(cudaSetDevice(rk[r].dev)); CK(cudaStreamSynchronize(rk[r].st)); } };
+    auto sync_all = [&]() { for (int r = 0; r < R; ++r) { CK(cudaSetDevice(rk[r].dev)); CK(cudaStreamSynchronize(rk[r].st)); CK(cudaStreamSynchronize(rk[r].cs)); } };
+    // where the result of the step with epoch `ep` lies on a rank
+    auto result_of = [&](Rank& k, unsigned ep) { return (comm == "pipelined" && R > 1 && (ep & 1)) ? k.y2 : k.y; };
 
     if (a.profile) { step_all(); step_all(); sync_all(); std::printf("[SUCCESS] profile launch done\n"); return 0; }
 
@@ -141,10 +168,11 @@ int main(int argc, char** argv)
     check_status();
     std::vector<uint16_t> ref((size_t)tokens * hidden), y0(ref.size()), yr(ref.size());
     CK(cudaMemcpy(ref.data(), rk[R].y, ref.size() * 2, cudaMemcpyDeviceToHost));
-    CK(cudaSetDevice(rk[0].dev)); CK(cudaMemcpy(y0.data(), rk[0].y, y0.size() * 2, cudaMemcpyDeviceToHost));
+    const unsigned ep_checked = epoch.load();
+    CK(cudaSetDevice(rk[0].dev)); CK(cudaMemcpy(y0.data(), result_of(rk[0], ep_checked), y0.size() * 2, cudaMemcpyDeviceToHost));
     bool replicas_equal = true;
     for (int r = 1; r < R; ++r) {
-        CK(cudaSetDevice(rk[r].dev)); CK(cudaMemcpy(yr.data(), rk[r].y, yr.size() * 2, cudaMemcpyDeviceToHost));
+        CK(cudaSetDevice(rk[r].dev)); CK(cudaMemcpy(yr.data(), result_of(rk[r], ep_checked), yr.size() * 2, cudaMemcpyDeviceToHost));
         replicas_equal = replicas_equal && std::memcmp(yr.data(), y0.data(), y0.size() * 2) == 0;
     }
     double num = 0, den = 0; float max_abs = 0, max_rel = 0;
@@ -170,7 +198,9 @@ int main(int argc, char** argv)
     for (int i = 0; i < iters; ++i) step_all();
     float worst = 0;
     for (int r = 0; r < R; ++r) {
-        CK(cudaSetDevice(rk[r].dev)); CK(cudaEventRecord(rk[r].e1, rk[r].st)); CK(cudaEventSynchronize(rk[r].e1));
+        CK(cudaSetDevice(rk[r].dev));
+        if (comm == "pipelined" && R > 1) { CK(cudaEventRecord(rk[r].gemm_done, rk[r].cs)); CK(cudaStreamWaitEvent(rk[r].st, rk[r].gemm_done, 0)); }   // the last all-reduce counts
+        CK(cudaEventRecord(rk[r].e1, rk[r].st)); CK(cudaEventSynchronize(rk[r].e1));
         float ms; CK(cudaEventElapsedTime(&ms, rk[r].e0, rk[r].e1)); worst = std::max(worst, ms);
     }
     check_status();

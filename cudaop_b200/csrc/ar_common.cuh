@@ -8,18 +8,14 @@
 namespace b200q {
 namespace arc {
 
+using ptx::st_release_sys;
+using ptx::ld_acquire_sys;
+using ptx::multimem_ld_reduce_f32x4;
+using ptx::multimem_ld_reduce_bf16x8;
+using ptx::multimem_st_bf16x8;
+
 constexpr int kMaxWorld = 16;
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v)
-{
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p)
-{
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 // Bounded wait until *flag has reached `epoch` (flags only grow; the signed difference tolerates
 // wrap-around).  On a timeout records (site, block) in *status and returns false.
 __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, uint32_t* status, uint32_t site)
@@ -39,28 +35,6 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
     return true;
 }
 
-// multimem.ld_reduce.add.v4.f32: the switch adds the same 16 bytes of every rank's buffer
-__device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc)
-{
-    float4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
-    return v;
-}
-// multimem.ld_reduce.add.acc::f32.v4.bf16x2: eight bf16 per rank added in the switch
-__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const __nv_bfloat16* mc)
-{
-    uint4 v;
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
-    return v;
-}
-// multimem.st.v4.bf16x2: one 16-byte store delivered to every rank's buffer
-__device__ __forceinline__ void multimem_st_bf16x8(__nv_bfloat16* mc, uint4 v)
-{
-    asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
-                 ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
 
 // Sum over ranks of eight consecutive partial values starting at element e, returned as eight
 // bf16 (one round-to-nearest-even of the fp32 sum).  MC: additions in the switch (their order and

@@ -138,7 +138,7 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 // bar.sync on a named barrier shared by the reducer warps only
 __device__ __forceinline__ void reducer_barrier()
 {
-    asm volatile("bar.sync 1, %0;" ::"n"(kReducerThreads) : "memory");
+    ptx::named_barrier_1<kReducerThreads>();
 }
 
 // The work of persistent CTA `cta` of `nctas` (the kernels below pass the block index and the grid size or,

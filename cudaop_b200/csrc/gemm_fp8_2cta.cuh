@@ -25,6 +25,8 @@
 namespace b200q {
 namespace fp8 {
 
+using ptx::tma_load_2d_pair;
+
 constexpr int kPairBM = 256;
 template <int BN>
 struct PairCfg {
@@ -36,14 +38,6 @@ struct PairCfg {
     static_assert(kStageBytes % 1024 == 0 && BN % 32 == 0, "tile shape");
 };
 
-// cp.async.bulk.tensor.2d with .cta_group::2: the completion barrier may live in the peer CTA of the pair
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* tm, uint32_t cluster_bar, int x, int y)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(cluster_bar), "r"(x), "r"(y)
-        : "memory");
-}
 
 template <int EPI, typename OutT, int BN>
 __global__ void __launch_bounds__(kBaseThreads, 1)
@@ -204,10 +198,8 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                             for (int j = 0; j < kCW / 8; ++j) {
                                 const uint32_t off = lane * kRowBytes + j * 16u;
                                 const uint32_t phys = off ^ (((off >> 7) & kSwzMask) << 4);
-                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbuf + phys),
-                                             "r"(pack_bf16x2(v[8 * j + 0], v[8 * j + 1])), "r"(pack_bf16x2(v[8 * j + 2], v[8 * j + 3])),
-                                             "r"(pack_bf16x2(v[8 * j + 4], v[8 * j + 5])), "r"(pack_bf16x2(v[8 * j + 6], v[8 * j + 7]))
-                                             : "memory");
+                                ptx::st_shared_v4(sbuf + phys, pack_bf16x2(v[8 * j + 0], v[8 * j + 1]), pack_bf16x2(v[8 * j + 2], v[8 * j + 3]),
+                                                 pack_bf16x2(v[8 * j + 4], v[8 * j + 5]), pack_bf16x2(v[8 * j + 6], v[8 * j + 7]));
                             }
                             ptx::fence_proxy_async_smem();
                             __syncwarp();

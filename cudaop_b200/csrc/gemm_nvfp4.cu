@@ -25,6 +25,8 @@
 namespace b200q {
 namespace nvfp4 {
 
+using ptx::bulk_load;
+
 constexpr int kBM = 128;
 constexpr int kBKBytes = 128;            // 256 E2M1 elements per row and stage
 constexpr int kBKElems = 256;
@@ -75,15 +77,6 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     const int r = tile - g * per_group;
     tm = first + r % rows;
     tn = r / rows;
-}
-
-// cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes: plain (untiled) bulk copy, no multicast;
-// both addresses 16-byte aligned, size a multiple of 16.
-__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
-                 : "memory");
 }
 
 template <int BN>

@@ -20,6 +20,11 @@
 namespace b200q {
 namespace nvfp4p {
 
+using ptx::tma_load_2d_pair;
+using ptx::tma_load_3d_pair;
+using ptx::tmem_cp_32x128b_warpx4_pair;
+using ptx::umma_mxf4nvf4_pair;
+
 constexpr int kBM = 128;                 // rows per CTA (256 per pair)
 constexpr int kBKBytes = 128;            // 256 E2M1 per row and stage
 constexpr int kBKElems = 256;
@@ -64,39 +69,6 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     const int r = tile - g * per_group;
     tm = first + r % rows;
     tn = r / rows;
-}
-
-// cp.async.bulk.tensor.2d with .cta_group::2 (no multicast): completion barrier may be the peer's
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* tm, uint32_t cluster_bar, int x, int y)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(cluster_bar), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tma_load_3d_pair(uint32_t smem_dst, const CUtensorMap* tm, uint32_t cluster_bar, int x, int y, int z)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(cluster_bar), "r"(x), "r"(y), "r"(z)
-        : "memory");
-}
-// tcgen05.cp.cta_group::2.32x128b.warpx4: both CTAs of the pair copy 32 rows x 16 bytes from their own
-// shared memory into their own tensor memory
-__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t smem_desc)
-{
-    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
-}
-// tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X
-__device__ __forceinline__ void umma_mxf4nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                   uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-        : "memory");
 }
 
 template <int BN>
@@ -268,8 +240,7 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     __syncwarp();
 #pragma unroll
                     for (int j = 0; j < 8; ++j)                        // 16-byte unit j of row `lane`, 128-byte swizzle
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbuf + lane * 128u + ((j ^ (lane & 7)) << 4)),
-                                     "r"(o[j].x), "r"(o[j].y), "r"(o[j].z), "r"(o[j].w) : "memory");
+                        ptx::st_shared_v4(sbuf + lane * 128u + ((j ^ (lane & 7)) << 4), o[j].x, o[j].y, o[j].z, o[j].w);
                     ptx::fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) { ptx::tma_store_2d_hint(&tmC, sbuf, col0, row0, store_policy); ptx::tma_store_commit(); }
@@ -342,6 +313,7 @@ extern "C" int b200q_nvfp4_set_group(int g)
 }
 // Called by b200q_gemm_nvfp4_blocked when the CTA-pair kernel is selected (b200q_nvfp4_set_2cta).
 namespace b200q {
+
 int gemm_nvfp4_blocked_pair(const void* Aq, const void* SFA_blocked, const void* Bq, const void* SFB_blocked,
                                              void* C, int M, int N, int K, float global_a, float global_b, int bn, void* stream)
 {

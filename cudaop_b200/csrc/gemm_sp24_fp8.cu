@@ -205,8 +205,7 @@ gemm_sp24_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     for (int j = 0; j < 4; ++j) {
                         const uint32_t off = lane * 64u + j * 16u;
                         const uint32_t phys = off ^ (((off >> 7) & 3u) << 4);           // 64-byte swizzle
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbuf + phys), "r"(o[j].x), "r"(o[j].y),
-                                     "r"(o[j].z), "r"(o[j].w) : "memory");
+                        ptx::st_shared_v4(sbuf + phys, o[j].x, o[j].y, o[j].z, o[j].w);
                     }
                     ptx::fence_proxy_async_smem();
                     __syncwarp();

@@ -18,6 +18,10 @@
 namespace b200q {
 namespace sp24p {
 
+using ptx::tma_load_2d_pair;
+using ptx::tmem_cp_128x128b_pair;
+using ptx::umma_sp_f8f6f4_pair;
+
 constexpr int kBM = 128;                 // rows per CTA (256 per pair)
 constexpr int kBN = 224;                 // tile columns
 constexpr int kBKLogical = 256;          // logical K per stage: 128 bytes of compressed A, 256 bytes of B per row
@@ -54,31 +58,6 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tn = r / rows;
 }
 
-// cp.async.bulk.tensor.2d with .cta_group::2 (no multicast): the completion barrier may be the peer's
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* tm, uint32_t cluster_bar, int x, int y)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(cluster_bar), "r"(x), "r"(y)
-        : "memory");
-}
-// tcgen05.cp.cta_group::2.128x128b: both CTAs copy 128 rows x 16 bytes from their own shared memory into four
-// columns of their own tensor memory
-__device__ __forceinline__ void tmem_cp_128x128b_pair(uint32_t taddr, uint64_t smem_desc)
-{
-    asm volatile("tcgen05.cp.cta_group::2.128x128b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
-}
-// tcgen05.mma.sp.cta_group::2.kind::f8f6f4
-__device__ __forceinline__ void umma_sp_f8f6f4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                                    uint32_t meta_tmem, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.sp.cta_group::2.kind::f8f6f4 [%0], %1, %2, [%5], %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(meta_tmem)
-        : "memory");
-}
 
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_sp24_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmE,
@@ -226,8 +205,7 @@ gemm_sp24_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
                     for (int j = 0; j < 4; ++j) {
                         const uint32_t off = lane * 64u + j * 16u;
                         const uint32_t phys = off ^ (((off >> 7) & 3u) << 4);           // 64-byte swizzle
-                        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(sbuf + phys), "r"(o[j].x), "r"(o[j].y),
-                                     "r"(o[j].z), "r"(o[j].w) : "memory");
+                        ptx::st_shared_v4(sbuf + phys, o[j].x, o[j].y, o[j].z, o[j].w);
                     }
                     ptx::fence_proxy_async_smem();
                     __syncwarp();

@@ -26,19 +26,13 @@
 namespace b200q {
 namespace w4a16 {
 
+using ptx::mma_bf16_16816;
+
 constexpr int kGroup = 128;
 constexpr int kWarps = 16;
 constexpr int kThreads = kWarps * 32;
 constexpr int kColsPerCta = 32;
 
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                               uint32_t b0, uint32_t b1)
-{
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 // nibbles (i, i+4) of a word, already offset to unsigned, -> two bf16 integers in [-8, 7]
 __device__ __forceinline__ uint32_t nib_pair_to_bf16(uint32_t w_unsigned, int shift)

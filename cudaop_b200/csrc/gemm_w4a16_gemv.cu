@@ -24,6 +24,11 @@
 namespace b200q {
 namespace w4gemv {
 
+using ptx::max_nan;
+using ptx::dp4a_uu;
+using ptx::dp4a_us;
+using ptx::bulk_load;
+
 constexpr int kGroup = 128;
 constexpr int kRows = 4;            // weight rows per warp
 constexpr int kSliceK = 1024;       // K covered by one warp-wide 16-byte load
@@ -77,8 +82,8 @@ w4a16_gemv_kernel(const __nv_bfloat16* __restrict__ X, const uint8_t* __restrict
     load_w(w, sc, k0);
 
     // 2. let the next kernel of the stream start its own weight stream; wait for the previous one before X
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
 
     float acc[kRows][MT];
 #pragma unroll
@@ -168,32 +173,6 @@ w4a16_gemv_kernel(const __nv_bfloat16* __restrict__ X, const uint8_t* __restrict
 // fp32.  About 1.1 instructions per weight instead of 3.
 constexpr int kMaxRows = 8;
 
-// max that returns NaN when either input is NaN (so a NaN activation reaches the exponent test below)
-__device__ __forceinline__ float max_nan(float a, float b)
-{
-    float d;
-    asm("max.NaN.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
-    return d;
-}
-// dp4a: four byte products added to a 32-bit accumulator; a unsigned bytes, b unsigned / signed bytes
-__device__ __forceinline__ int dp4a_uu(uint32_t a, uint32_t b, int c)
-{
-    int d;
-    asm("dp4a.u32.u32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c)
-{
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-    return d;
-}
-__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
-                 : "memory");
-}
 
 template <int MT>
 __global__ void __launch_bounds__(256)
@@ -225,8 +204,8 @@ w4a16_gemv_smem_kernel(const __nv_bfloat16* __restrict__ X, const uint8_t* __res
     for (int i = tid; i < nrows * G; i += nthreads) s_sm[i] = __ldg(S + static_cast<size_t>(n0) * G + i);
 
     // 2. the next call may start now (its CTAs fit beside these); wait for the previous one before X
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
 
     float acc[kMaxRows][MT];
 #pragma unroll

@@ -32,6 +32,14 @@
 namespace b200q {
 namespace w4tc {
 
+using ptx::tmem_st_32x32b_x16;
+using ptx::tmem_st_wait;
+using ptx::tmem_ld_32x32b_x8;
+using ptx::umma_f16_ts;
+using ptx::pdl_launch_dependents;
+using ptx::pdl_wait;
+using ptx::ld_dsmem_f32;
+
 constexpr int kRows = 128;          // weight rows per CTA (UMMA M)
 constexpr int kTok = 16;            // tokens per pass (UMMA N)
 constexpr int kGroup = 128;         // K per scale group
@@ -59,49 +67,6 @@ struct Params {
     int groups_total, groups_per_cta;
     uint32_t* status;
 };
-
-// tcgen05.st.sync.aligned.32x32b.x16.b32: 16 consecutive 32-bit columns of the thread's own lane
-__device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_t (&r)[16])
-{
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-// tcgen05.ld.sync.aligned.32x32b.x8.b32
-__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8])
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr) : "memory");
-}
-
-// tcgen05.mma.cta_group::1.kind::f16 with the A operand in tensor memory
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// griddepcontrol: programmatic dependent launch.  launch_dependents lets the next kernel of the
-// stream start its own prologue and weight fetch; wait blocks until the previous kernel's
-// results (this call's activations) are visible.
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-__device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr)
-{
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr));
-    return v;
-}
 
 __global__ void __launch_bounds__(kThreads, 1)
 w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
@@ -387,6 +352,7 @@ int g_pdl = 0;       // programmatic dependent launch (b200q_w4a16_set_pdl) of t
 extern "C" int b200q_gemm_w4a16_warp_mma(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K,
                                          int group, void* stream);
 namespace b200q {
+
 // gemm_w4a16_gemv.cu: CUDA-core kernel for M <= 4
 int gemm_w4a16_gemv(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, int pdl, int form,
                     void* stream);
