@@ -329,6 +329,22 @@ def gemm_cases(peaks):
                          "frac_4x_measured_bf16": tf / (4.0 * peaks["bf16_tflops"])}
     del A4, B4, sfa, sfb, sfa_rm, sfb_rm
     torch.cuda.synchronize(); time.sleep(1.5)
+    # MXFP8 8192^3 (E4M3 data, one UE8M0 scale per 32 K; scales pre-blocked)
+    xa = torch.randn((S, S // 32, 32), device="cuda", generator=gen); xb = torch.randn((S, S // 32, 32), device="cuda", generator=gen)
+
+    def mx(x):
+        e = torch.floor(torch.log2(x.abs().amax(-1).clamp_min(2.0 ** -100))) - 8.0
+        q = (x * torch.exp2(-e).unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+        return q.view(S, S).contiguous(), (e + 127.0).to(torch.uint8).contiguous()
+    A8, sa8 = mx(xa); B8, sb8 = mx(xb)
+    del xa, xb
+    sa8b = ops.mxfp8_swizzle_sf(sa8, S); sb8b = ops.mxfp8_swizzle_sf(sb8, S)
+    ms = time_loop(lambda: L.b200q_gemm_mxfp8_blocked(A8.data_ptr(), sa8b.data_ptr(), B8.data_ptr(), sb8b.data_ptr(), c.data_ptr(),
+                                                      S, S, S, st()), 20)
+    tf = 2 * S ** 3 / ms / 1e9
+    out["mxfp8_8192"] = {"ms": ms, "tflops": tf, "frac_nominal_4500": tf / NOMINAL["fp8_tflops"], "frac_2x_measured_bf16": tf / fp8_meas}
+    del A8, B8, sa8, sb8, sa8b, sb8b
+    torch.cuda.synchronize(); time.sleep(1.5)
     # 2:4 sparse FP8 4096 x 8192 x 8192 (dense-equivalent FLOPs)
     Ms = 4096
     Ac, Em, ssa = _sparse24_normal(Ms, S, gen)

@@ -22,6 +22,7 @@ _lib = None
 
 __all__ = [
     "lib", "gemm_fp8", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "gemm_nvfp4", "nvfp4_swizzle_sf",
+    "gemm_mxfp8", "mxfp8_swizzle_sf",
     "gemm_sparse_fp8", "quant_rows_e4m3", "status", "check_status", "set_wait_limit_ms", "WaitTimeout", "LIB_PATH",
 ]
 
@@ -29,6 +30,8 @@ _VP, _I, _F = C.c_void_p, C.c_int, C.c_float
 _SIZE_T_FUNCS = {
     "b200q_gemm_nvfp4_workspace_bytes": [C.c_int, C.c_int, C.c_int],
     "b200q_nvfp4_sf_bytes": [C.c_int, C.c_int],
+    "b200q_mxfp8_sf_bytes": [C.c_int, C.c_int],
+    "b200q_gemm_mxfp8_workspace_bytes": [C.c_int, C.c_int, C.c_int],
     "b200q_gemm_nvfp4_static_max_bytes": [],
     "b200q_allreduce_signal_bytes": [],
     "b200q_rank_barrier_signal_bytes": [],
@@ -44,6 +47,10 @@ _SIGNATURES = {
     "b200q_gemm_nvfp4_static": [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
     "b200q_gemm_nvfp4_blocked": [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
     "b200q_nvfp4_swizzle_sf": [_VP, _VP, _I, _I, _VP],
+    "b200q_gemm_mxfp8": [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _VP, _VP],
+    "b200q_gemm_mxfp8_blocked": [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _VP],
+    "b200q_mxfp8_swizzle_sf": [_VP, _VP, _I, _I, _VP],
+    "b200q_mxfp8_set_tile_n": [_I],
     "b200q_nvfp4_set_tile_n": [_I],
     "b200q_nvfp4_set_2cta": [_I],
     "b200q_fp8_set_tma_store": [_I],
@@ -118,7 +125,7 @@ def _check(t: torch.Tensor, name: str, dtypes, ndim: int) -> None:
 # signatures with defaults, as op/grouped_gemm/cudaop_grouped_gemm/ops.py does for its _C module.
 
 EXTENSION_OPS = ("gemm_fp8", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "nvfp4_swizzle_sf", "gemm_nvfp4",
-                 "gemm_sparse_fp8", "quant_rows_e4m3")
+                 "mxfp8_swizzle_sf", "gemm_mxfp8", "gemm_sparse_fp8", "quant_rows_e4m3")
 try:
     from . import _C                                    # noqa: F401
     _C_ERROR = None
@@ -167,6 +174,17 @@ def gemm_nvfp4(aq, sfa, bq, sfb, global_a: float, global_b: float, blocked: bool
     allocated per call) or the output of :func:`nvfp4_swizzle_sf` (``blocked=True``).
     """
     return _ext().gemm_nvfp4(aq, sfa, bq, sfb, float(global_a), float(global_b), bool(blocked))
+
+
+def mxfp8_swizzle_sf(sf: torch.Tensor, K: int) -> torch.Tensor:
+    """Row-major UE8M0 scales [rows, K/32] -> the blocked layout the MXFP8 GEMM reads."""
+    return _ext().mxfp8_swizzle_sf(sf, int(K))
+
+
+def gemm_mxfp8(a, sfa, b, sfb, blocked: bool = False) -> torch.Tensor:
+    """C[M,N] (bf16) for MXFP8 operands: E4M3 bytes [rows, K] with one UE8M0 scale per 32 K ([rows, K/32], or the
+    output of :func:`mxfp8_swizzle_sf` with ``blocked=True``)."""
+    return _ext().gemm_mxfp8(a, sfa, b, sfb, bool(blocked))
 
 
 def gemm_sparse_fp8(a_comp, a_meta, b, scale_a: float, scale_b: float) -> torch.Tensor:

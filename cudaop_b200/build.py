@@ -93,13 +93,14 @@ def build_ext(force: bool = False) -> str:
             sys.stderr.write(r.stdout)
             raise RuntimeError("building cudaop_b200._C failed")
         found = glob.glob(os.path.join(HERE, "_C*.so"))
-    if ROOT not in sys.path:
-        sys.path.insert(0, ROOT)
-    import importlib
-    ops = importlib.import_module("cudaop_b200")
-    missing = [n for n in ops.EXTENSION_OPS if not callable(getattr(ops._C, n, None))]
-    if missing:
-        raise RuntimeError(f"cudaop_b200._C does not export {missing}")
+    # import check in a fresh interpreter (this process may hold an older copy of the module)
+    code = ("import sys; sys.path.insert(0, %r); import cudaop_b200 as ops; "
+            "missing = [n for n in ops.EXTENSION_OPS if not callable(getattr(ops._C, n, None))]; "
+            "assert ops._C is not None, ops._C_ERROR; assert not missing, missing" % ROOT)
+    r = subprocess.run([sys.executable, "-c", code], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout)
+        raise RuntimeError("cudaop_b200._C does not import or lacks operators")
     return found[0]
 
 

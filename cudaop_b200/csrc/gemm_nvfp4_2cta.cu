@@ -1,4 +1,11 @@
-// NVFP4 block-scaled GEMM on CTA pairs (tcgen05 cta_group::2): 256 x BN output tile per pair.
+// Block-scaled GEMMs on CTA pairs (tcgen05 cta_group::2): 256 x BN output tile per pair.
+//   FMT 0  NVFP4: E2M1 data, one UE4M3 scale per 16 K, kind::mxf4nvf4.block_scale.scale_vec::4X (256 x BN x 64)
+//   FMT 1  MXFP8: E4M3 data, one UE8M0 scale per 32 K, kind::mxf8f6f4.block_scale           (256 x BN x 32)
+//          (the reference's other block-scaled format: op/test/arch_primitives/ptx_mma_fp8.cu:126-178,
+//          scale decoder op/test/arch_primitives/ptx_mma_fp6.cu:344-351)
+// Both keep a 128-byte K slab per row and stage and the same blocked scale layout (512-byte blocks of 128
+// rows x 4 scales); a block covers 64 K for NVFP4 (one MMA) and 128 K for MXFP8 (four MMAs, which pick their
+// scale byte with the scale-factor id of the instruction descriptor).  The text below describes NVFP4.
 //
 // Same arithmetic and operand formats as gemm_nvfp4.cu (E2M1 data, one UE4M3 scale per 16 K in the
 // blocked layout, fp32 accumulate, global scales in the epilogue; formats:
@@ -24,31 +31,37 @@ using ptx::tma_load_2d_pair;
 using ptx::tma_load_3d_pair;
 using ptx::tmem_cp_32x128b_warpx4_pair;
 using ptx::umma_mxf4nvf4_pair;
+using ptx::umma_mxf8f6f4_pair;
+
+constexpr int kFmtNvfp4 = 0, kFmtMxfp8 = 1;
 
 constexpr int kBM = 128;                 // rows per CTA (256 per pair)
-constexpr int kBKBytes = 128;            // 256 E2M1 per row and stage
-constexpr int kBKElems = 256;
+constexpr int kBKBytes = 128;            // per row and stage: 256 E2M1 or 128 E4M3
 constexpr int kThreads = 320;            // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two per TMEM lane quadrant)
 constexpr int kSfBlockBytes = 512;
 constexpr uint32_t kTmemCols = 512;
 
-template <int BN>
+template <int BN, int FMT>
 struct Cfg {
     static_assert(BN % 64 == 0 && BN <= 256, "B tile width");
+    static constexpr int kBKElems = (FMT == kFmtMxfp8) ? 128 : 256;  // K elements per stage
+    static constexpr int kSfBlocks = (FMT == kFmtMxfp8) ? 1 : 4;     // 512-byte scale blocks per row block and stage
     static constexpr int kMaxOff = (BN % 128 == 0) ? 0 : 64;
     static constexpr int kNB = (kMaxOff + BN + 127) / 128;           // scale row-blocks of the whole B tile
     static constexpr int kABytes = kBM * kBKBytes;
     static constexpr int kBHalfBytes = (BN / 2) * kBKBytes;
-    static constexpr int kSfaBytes = 4 * kSfBlockBytes;
-    static constexpr int kSfbBytes = kNB * 4 * kSfBlockBytes;
-    static constexpr int kStageBytes = kABytes + kBHalfBytes + kSfaBytes + kSfbBytes;
+    static constexpr int kSfaBytes = kSfBlocks * kSfBlockBytes;
+    static constexpr int kSfbBytes = kNB * kSfBlocks * kSfBlockBytes;
+    static constexpr int kLoadBytes = kABytes + kBHalfBytes + kSfaBytes + kSfbBytes;      // what the TMA loads bring per CTA
+    static constexpr int kStageBytes = (kLoadBytes + 1023) / 1024 * 1024;                 // operand tiles start 1024-byte aligned
     static constexpr int kStoreBytes = 8 * 4096;                     // per epilogue warp one 32-row x 64-column bf16 staging buffer
     static constexpr int kStages = (227 * 1024 - 1024 - 256 - kStoreBytes) / kStageBytes > 6 ? 6 : (227 * 1024 - 1024 - 256 - kStoreBytes) / kStageBytes;
     static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
-    static constexpr int kAccBufs = (2 * BN + 16 + 16 * kNB <= 512) ? 2 : 1;
+    static constexpr int kSfCols = 4 * kSfBlocks;                    // TMEM columns of one row block's scales of a stage
+    static constexpr int kAccBufs = (2 * BN + kSfCols + kSfCols * kNB <= 512) ? 2 : 1;
     static constexpr int kSfaCol = kAccBufs * BN;
-    static constexpr int kSfbCol = kSfaCol + 16;
-    static_assert(kStageBytes % 1024 == 0, "stage alignment");
+    static constexpr int kSfbCol = kSfaCol + kSfCols;
+    static_assert(FMT == kFmtMxfp8 || kLoadBytes % 1024 == 0, "stage alignment");
 };
 
 struct Params {
@@ -71,14 +84,15 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     tn = r / rows;
 }
 
-template <int BN>
+template <int BN, int FMT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                        const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                        const __grid_constant__ CUtensorMap tmC, const Params p)
 {
-    using C = Cfg<BN>;
+    using C = Cfg<BN, FMT>;
     constexpr int kStages = C::kStages;
+    constexpr int kBKElems = C::kBKElems;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t store_base = smem_base + kStages * C::kStageBytes;      // epilogue staging, 1024-byte aligned
@@ -95,7 +109,7 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     const uint32_t cta_rank = ptx::cluster_ctarank();
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const int num_kb = (p.K + kBKElems - 1) / kBKElems;
-    const int k64_total = p.K / 64;
+    const int ksteps_total = p.K / (FMT == kFmtMxfp8 ? 32 : 64);     // MMAs along K
     const int num_tiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
@@ -127,13 +141,13 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                     const uint32_t sa = smem_base + stage * C::kStageBytes;
                     const uint32_t sb = sa + C::kABytes, ssfa = sb + C::kBHalfBytes, ssfb = ssfa + C::kSfaBytes;
                     const uint32_t leader_full = ptx::mapa(full_bar(stage), 0);
-                    if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * C::kStageBytes);
+                    if (cta_rank == 0) ptx::mbar_arrive_expect_tx(full_bar(stage), 2 * C::kLoadBytes);
                     tma_load_2d_pair(sa, &tmA, leader_full, kb * kBKBytes, m0);
                     tma_load_2d_pair(sb, &tmB, leader_full, kb * kBKBytes, n0 + static_cast<int>(cta_rank) * (BN / 2));
                     // scales: the blocked arrays as [row block][K/64 * 2 rows of 256 bytes]; a K slab is 8 such rows,
                     // and one box takes them for all row blocks of the B tile at once
-                    tma_load_3d_pair(ssfa, &tmSFA, leader_full, 0, 8 * kb, mb);
-                    tma_load_3d_pair(ssfb, &tmSFB, leader_full, 0, 8 * kb, rb0);
+                    tma_load_3d_pair(ssfa, &tmSFA, leader_full, 0, 2 * C::kSfBlocks * kb, mb);
+                    tma_load_3d_pair(ssfb, &tmSFB, leader_full, 0, 2 * C::kSfBlocks * kb, rb0);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -142,7 +156,10 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     } else if (warp == 1) {
         // ---------------------------------------------------------- MMA issuer (leader only)
         if (cta_rank == 0 && ptx::elect_one()) {
-            constexpr uint32_t idesc = ptx::umma_idesc_block_scaled(1, 1, 2 * kBM, BN, 0, 0, 0);
+            // NVFP4: E2M1 (format 1 of kind::mxf4nvf4) with UE4M3 scales; MXFP8: E4M3 (format 0 of kind::mxf8f6f4) with
+            // UE8M0 scales, scale-factor ids filled in per MMA
+            constexpr uint32_t idesc = (FMT == kFmtMxfp8) ? ptx::umma_idesc_block_scaled(0, 0, 2 * kBM, BN, 0, 0, 1)
+                                                          : ptx::umma_idesc_block_scaled(1, 1, 2 * kBM, BN, 0, 0, 0);
             int stage = 0; uint32_t phase = 0; bool ok = true;
             int t = 0;
             for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
@@ -156,26 +173,44 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(full_bar(stage), phase, p.status, 3)) { ok = false; break; }
                     ptx::tcgen05_fence_after_sync();
-                    const int ksteps = min(4, k64_total - 4 * kb);
+                    const int ksteps = min(4, ksteps_total - 4 * kb);
                     const uint32_t sa = smem_base + stage * C::kStageBytes;
                     const uint32_t sb = sa + C::kABytes, ssfa = sb + C::kBHalfBytes, ssfb = ssfa + C::kSfaBytes;
                     const uint64_t da = ptx::smem_desc_sw128_kmajor(sa), db = ptx::smem_desc_sw128_kmajor(sb);
                     const uint64_t dsfa = ptx::smem_desc_noswizzle_kmajor(ssfa, 16, 128), dsfb = ptx::smem_desc_noswizzle_kmajor(ssfb, 16, 128);
                     const uint32_t tsfa = tmem_base + C::kSfaCol, tsfb = tmem_base + C::kSfbCol;
-                    auto kstep = [&](int ks) {
-                        // descriptors advance in 16-byte units: one 512-byte scale block = 32
-                        tmem_cp_32x128b_warpx4_pair(tsfa + 4 * ks, dsfa + 32u * ks);
+                    if constexpr (FMT == kFmtMxfp8) {
+                        // one scale block per row block serves the four MMAs of the slab: byte ks of every 32-bit scale
+                        // column belongs to MMA ks (scale-factor ids in bits [4,6) and [29,31) of the descriptor)
+                        tmem_cp_32x128b_warpx4_pair(tsfa, dsfa);
 #pragma unroll
-                        for (int i = 0; i < C::kNB; ++i)
-                            tmem_cp_32x128b_warpx4_pair(tsfb + 4 * C::kNB * ks + 4 * i, dsfb + 32u * (i * 4 + ks));
-                        umma_mxf4nvf4_pair(d_tmem, da + 2u * ks, db + 2u * ks, idesc, tsfa + 4 * ks,
-                                           tsfb + 4 * C::kNB * ks + sfb_col_off, (kb | ks) != 0);
-                    };
-                    if (ksteps == 4) {
+                        for (int i = 0; i < C::kNB; ++i) tmem_cp_32x128b_warpx4_pair(tsfb + 4 * i, dsfb + 32u * i);
+                        auto kstep = [&](int ks) {
+                            const uint32_t id = idesc | (static_cast<uint32_t>(ks) << 4) | (static_cast<uint32_t>(ks) << 29);
+                            umma_mxf8f6f4_pair(d_tmem, da + 2u * ks, db + 2u * ks, id, tsfa, tsfb + sfb_col_off, (kb | ks) != 0);
+                        };
+                        if (ksteps == 4) {
 #pragma unroll
-                        for (int ks = 0; ks < 4; ++ks) kstep(ks);
+                            for (int ks = 0; ks < 4; ++ks) kstep(ks);
+                        } else {
+                            for (int ks = 0; ks < ksteps; ++ks) kstep(ks);
+                        }
                     } else {
-                        for (int ks = 0; ks < ksteps; ++ks) kstep(ks);
+                        auto kstep = [&](int ks) {
+                            // descriptors advance in 16-byte units: one 512-byte scale block = 32
+                            tmem_cp_32x128b_warpx4_pair(tsfa + 4 * ks, dsfa + 32u * ks);
+#pragma unroll
+                            for (int i = 0; i < C::kNB; ++i)
+                                tmem_cp_32x128b_warpx4_pair(tsfb + 4 * C::kNB * ks + 4 * i, dsfb + 32u * (i * 4 + ks));
+                            umma_mxf4nvf4_pair(d_tmem, da + 2u * ks, db + 2u * ks, idesc, tsfa + 4 * ks,
+                                               tsfb + 4 * C::kNB * ks + sfb_col_off, (kb | ks) != 0);
+                        };
+                        if (ksteps == 4) {
+#pragma unroll
+                            for (int ks = 0; ks < 4; ++ks) kstep(ks);
+                        } else {
+                            for (int ks = 0; ks < ksteps; ++ks) kstep(ks);
+                        }
                     }
                     ptx::umma_commit_2cta(empty_bar(stage), 3);
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -271,17 +306,17 @@ gemm_nvfp4_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     }
 }
 
-template <int BN>
+template <int BN, int FMT>
 cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA, const CUtensorMap& tmSFB,
                    const CUtensorMap& tmC, Params p, cudaStream_t stream)
 {
-    auto kernel = gemm_nvfp4_2cta_kernel<BN>;
+    auto kernel = gemm_nvfp4_2cta_kernel<BN, FMT>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::kSmemBytes);
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN, FMT>::kSmemBytes);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
@@ -293,7 +328,7 @@ cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtenso
     const int pairs = tiles < sms / 2 ? tiles : sms / 2;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = Cfg<BN>::kSmemBytes; cfg.stream = stream;
+    cfg.dynamicSmemBytes = Cfg<BN, FMT>::kSmemBytes; cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
@@ -311,33 +346,42 @@ extern "C" int b200q_nvfp4_set_group(int g)
     b200q::nvfp4p::g_group = g;
     return 0;
 }
-// Called by b200q_gemm_nvfp4_blocked when the CTA-pair kernel is selected (b200q_nvfp4_set_2cta).
+// Called by b200q_gemm_nvfp4_blocked (fmt 0, when the CTA-pair kernel is selected with b200q_nvfp4_set_2cta) and by
+// b200q_gemm_mxfp8_blocked (fmt 1).  Operand rows hold K/2 bytes (NVFP4) or K bytes (MXFP8); the blocked scale arrays
+// hold one 512-byte block per 128 rows and per 64 K (NVFP4) / 128 K (MXFP8).
 namespace b200q {
 
-int gemm_nvfp4_blocked_pair(const void* Aq, const void* SFA_blocked, const void* Bq, const void* SFB_blocked,
-                                             void* C, int M, int N, int K, float global_a, float global_b, int bn, void* stream)
+int gemm_block_scaled_pair(int fmt, const void* Aq, const void* SFA_blocked, const void* Bq, const void* SFB_blocked,
+                           void* C, int M, int N, int K, float alpha, int bn, void* stream)
 {
+    using namespace nvfp4p;
     if (Aq == nullptr || SFA_blocked == nullptr || Bq == nullptr || SFB_blocked == nullptr || C == nullptr)
         return cudaErrorInvalidValue;
-    if (M <= 0 || N <= 0 || K <= 0 || K % 64 != 0) return cudaErrorInvalidValue;
+    if (fmt != kFmtNvfp4 && fmt != kFmtMxfp8) return cudaErrorInvalidValue;
+    if (M <= 0 || N <= 0 || K <= 0 || K % (fmt == kFmtMxfp8 ? 32 : 64) != 0) return cudaErrorInvalidValue;
     if (!aligned16(Aq) || !aligned16(Bq) || !aligned16(SFA_blocked) || !aligned16(SFB_blocked)) return cudaErrorInvalidValue;
     if (bn != 192 && bn != 256) return cudaErrorInvalidValue;
-    nvfp4p::Params p{};
-    p.M = M; p.N = N; p.K = K; p.C = static_cast<__nv_bfloat16*>(C); p.alpha = global_a * global_b;
+    const size_t row_bytes = fmt == kFmtMxfp8 ? static_cast<size_t>(K) : static_cast<size_t>(K) / 2;
+    if (row_bytes % 16 != 0) return cudaErrorInvalidValue;
+    Params p{};
+    p.M = M; p.N = N; p.K = K; p.C = static_cast<__nv_bfloat16*>(C); p.alpha = alpha;
     p.status = status_ptr();
     if (p.status == nullptr) return cudaErrorInvalidDevice;
-    p.group = nvfp4p::g_group > 0 ? nvfp4p::g_group
-                                  : choose_tile_group((M + 2 * nvfp4p::kBM - 1) / (2 * nvfp4p::kBM), 2 * nvfp4p::kBM, static_cast<size_t>(K) / 2);
+    p.group = g_group > 0 ? g_group : choose_tile_group((M + 2 * kBM - 1) / (2 * kBM), 2 * kBM, row_bytes);
     CUtensorMap tmA, tmB, tmSFA, tmSFB;
-    if (!make_tmap_2d_u8(&tmA, Aq, M, K / 2, K / 2, nvfp4p::kBM, nvfp4p::kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
-    if (!make_tmap_2d_u8(&tmB, Bq, N, K / 2, K / 2, bn / 2, nvfp4p::kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
+    if (!make_tmap_2d_u8(&tmA, Aq, M, row_bytes, row_bytes, kBM, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
+    if (!make_tmap_2d_u8(&tmB, Bq, N, row_bytes, row_bytes, bn / 2, kBKBytes, CU_TENSOR_MAP_SWIZZLE_128B)) return cudaErrorInvalidValue;
     {
-        const uint64_t k_rows = static_cast<uint64_t>(K / 64) * 2;                 // 256-byte rows per row block
+        // the blocked scale arrays as [row block][2 * blocks along K][256 bytes]; one box takes the blocks of a
+        // K slab for all row blocks of the B tile at once
+        const uint64_t blocks_k = fmt == kFmtMxfp8 ? static_cast<uint64_t>((K + 127) / 128) : static_cast<uint64_t>(K / 64);
+        const uint32_t slab_rows = fmt == kFmtMxfp8 ? 2u : 8u;
+        const uint64_t k_rows = blocks_k * 2;
         const uint64_t strides[2] = {256, k_rows * 256};
         const uint64_t dims_a[3] = {256, k_rows, static_cast<uint64_t>((M + 127) / 128)};
         const uint64_t dims_b[3] = {256, k_rows, static_cast<uint64_t>((N + 127) / 128)};
-        const uint32_t box_a[3] = {256, 8, 1};
-        const uint32_t box_b[3] = {256, 8, static_cast<uint32_t>(bn == 192 ? nvfp4p::Cfg<192>::kNB : nvfp4p::Cfg<256>::kNB)};
+        const uint32_t box_a[3] = {256, slab_rows, 1};
+        const uint32_t box_b[3] = {256, slab_rows, static_cast<uint32_t>(bn == 192 ? Cfg<192, 0>::kNB : Cfg<256, 0>::kNB)};
         if (encode_tiled(&tmSFA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, SFA_blocked, dims_a, strides, box_a, CU_TENSOR_MAP_SWIZZLE_NONE) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
         if (encode_tiled(&tmSFB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, SFB_blocked, dims_b, strides, box_b, CU_TENSOR_MAP_SWIZZLE_NONE) != CUDA_SUCCESS)
@@ -355,7 +399,14 @@ int gemm_nvfp4_blocked_pair(const void* Aq, const void* SFA_blocked, const void*
             return cudaErrorInvalidValue;
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (bn == 192) return nvfp4p::launch<192>(tmA, tmB, tmSFA, tmSFB, tmC, p, s);
-    return nvfp4p::launch<256>(tmA, tmB, tmSFA, tmSFB, tmC, p, s);
+    if (fmt == kFmtMxfp8)
+        return bn == 192 ? launch<192, kFmtMxfp8>(tmA, tmB, tmSFA, tmSFB, tmC, p, s) : launch<256, kFmtMxfp8>(tmA, tmB, tmSFA, tmSFB, tmC, p, s);
+    return bn == 192 ? launch<192, kFmtNvfp4>(tmA, tmB, tmSFA, tmSFB, tmC, p, s) : launch<256, kFmtNvfp4>(tmA, tmB, tmSFA, tmSFB, tmC, p, s);
+}
+
+int gemm_nvfp4_blocked_pair(const void* Aq, const void* SFA_blocked, const void* Bq, const void* SFB_blocked,
+                            void* C, int M, int N, int K, float global_a, float global_b, int bn, void* stream)
+{
+    return gemm_block_scaled_pair(nvfp4p::kFmtNvfp4, Aq, SFA_blocked, Bq, SFB_blocked, C, M, N, K, global_a * global_b, bn, stream);
 }
 }  // namespace b200q

@@ -495,6 +495,18 @@ __device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint
     asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
 }
 
+// tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X: 8-bit (or narrower) float operands with one
+// UE8M0 scale per 32 K-elements; the byte of the 32-bit TMEM scale column is chosen by the scale-factor ids of idesc
+__device__ __forceinline__ void umma_mxf8f6f4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale.scale_vec::1X [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
 // tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X
 __device__ __forceinline__ void umma_mxf4nvf4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                    uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate)

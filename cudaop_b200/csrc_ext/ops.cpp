@@ -155,6 +155,41 @@ torch::Tensor gemm_nvfp4(torch::Tensor aq, torch::Tensor sfa, torch::Tensor bq, 
     return c;
 }
 
+torch::Tensor mxfp8_swizzle_sf(torch::Tensor sf, int64_t K)
+{
+    check_cuda_2d(sf, "sf", {kU8});
+    TORCH_CHECK_VALUE(sf.size(1) * 32 == K, "scales must be [rows, K/32]");
+    const c10::cuda::CUDAGuard guard(sf.device());
+    auto out = out_like(sf, {(int64_t)b200q_mxfp8_sf_bytes((int)sf.size(0), (int)K)}, kU8);
+    raise_on(b200q_mxfp8_swizzle_sf(sf.data_ptr(), out.data_ptr(), (int)sf.size(0), (int)K, stream_of(sf)), "b200q_mxfp8_swizzle_sf");
+    return out;
+}
+
+torch::Tensor gemm_mxfp8(torch::Tensor a, torch::Tensor sfa, torch::Tensor b, torch::Tensor sfb, bool blocked)
+{
+    check_cuda_2d(a, "a", {kU8, kE4M3}); check_cuda_2d(b, "b", {kU8, kE4M3});
+    const int64_t M = a.size(0), N = b.size(0), K = a.size(1);
+    TORCH_CHECK_VALUE(b.size(1) == K && K % 32 == 0, "shape mismatch (K must match and be a multiple of 32)");
+    const c10::cuda::CUDAGuard guard(a.device());
+    auto c = out_like(a, {M, N}, kBF16);
+    if (blocked) {
+        check_cuda_2d(sfa, "sfa", {kU8}, 1); check_cuda_2d(sfb, "sfb", {kU8}, 1);
+        same_device({&a, &sfa, &b, &sfb});
+        TORCH_CHECK_VALUE(sfa.numel() == (int64_t)b200q_mxfp8_sf_bytes((int)M, (int)K) && sfb.numel() == (int64_t)b200q_mxfp8_sf_bytes((int)N, (int)K),
+                          "blocked scale arrays have the wrong size");
+        raise_on(b200q_gemm_mxfp8_blocked(a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K,
+                                          stream_of(a)), "b200q_gemm_mxfp8_blocked");
+        return c;
+    }
+    check_cuda_2d(sfa, "sfa", {kU8}); check_cuda_2d(sfb, "sfb", {kU8});
+    same_device({&a, &sfa, &b, &sfb});
+    TORCH_CHECK_VALUE(sfa.size(0) == M && sfa.size(1) == K / 32 && sfb.size(0) == N && sfb.size(1) == K / 32, "shape mismatch");
+    auto ws = out_like(a, {(int64_t)b200q_gemm_mxfp8_workspace_bytes((int)M, (int)N, (int)K)}, kU8);
+    raise_on(b200q_gemm_mxfp8(a.data_ptr(), sfa.data_ptr(), b.data_ptr(), sfb.data_ptr(), c.data_ptr(), (int)M, (int)N, (int)K,
+                              ws.data_ptr(), stream_of(a)), "b200q_gemm_mxfp8");
+    return c;
+}
+
 torch::Tensor gemm_sparse_fp8(torch::Tensor a_comp, torch::Tensor a_meta, torch::Tensor b, double scale_a, double scale_b)
 {
     check_cuda_2d(a_comp, "a_comp", {kU8, kE4M3}); check_cuda_2d(a_meta, "a_meta", {kU8}); check_cuda_2d(b, "b", {kU8, kE4M3});
@@ -187,6 +222,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("gemm_w4a16", &gemm_w4a16, "INT4 weight-only GEMM, bf16 activations");
     m.def("nvfp4_swizzle_sf", &nvfp4_swizzle_sf, "row-major UE4M3 scales -> blocked layout");
     m.def("gemm_nvfp4", &gemm_nvfp4, "NVFP4 block-scaled GEMM");
+    m.def("mxfp8_swizzle_sf", &mxfp8_swizzle_sf, "row-major UE8M0 scales -> blocked layout");
+    m.def("gemm_mxfp8", &gemm_mxfp8, "MXFP8 block-scaled GEMM");
     m.def("gemm_sparse_fp8", &gemm_sparse_fp8, "2:4-sparse FP8 GEMM");
     m.def("quant_rows_e4m3", &quant_rows_e4m3, "bf16 rows -> E4M3 + per-row fp32 scale");
 }

@@ -91,6 +91,23 @@ int b200q_gemm_nvfp4_blocked(const void* Aq, const void* SFA_blocked, const void
 int b200q_nvfp4_swizzle_sf(const void* sf_rowmajor, void* sf_blocked, int rows, int K, void* stream);
 size_t b200q_nvfp4_sf_bytes(int rows, int K);      /* size of one blocked scale array */
 
+/* MXFP8 block-scaled GEMM: C(bf16) = ((A . 2^(sfa-127)) * (B . 2^(sfb-127))^T).  A[M,K], B[N,K]: E4M3 bytes;
+ * SFA[M,K/32], SFB[N,K/32]: one UE8M0 scale byte per 32 consecutive K, row-major (value 2^(byte - 127), 0xFF = NaN).
+ * This is the reference's kind::mxf8f6f4.block_scale.scale_vec::1X arithmetic
+ * (op/test/arch_primitives/ptx_mma_fp8.cu:126-178, scale decoder op/test/arch_primitives/ptx_mma_fp6.cu:344-351) as a
+ * whole GEMM.  Requires K % 32 == 0 and 16-byte aligned pointers.  `workspace`: caller-owned scratch of
+ * b200q_gemm_mxfp8_workspace_bytes(M,N,K) bytes for the blocked copies of both scale arrays. */
+int b200q_gemm_mxfp8(const void* A, const void* SFA, const void* B, const void* SFB, void* C, int M, int N, int K,
+                     void* workspace, void* stream);
+size_t b200q_gemm_mxfp8_workspace_bytes(int M, int N, int K);
+/* The same on scales already in the blocked layout: [ceil(rows/128)][ceil(K/128)] blocks of 512 bytes; inside a
+ * block the scales of row r for the four 32-K steps of the 128-K slab sit at bytes (r % 32) * 16 + (r / 32) * 4 + j. */
+int b200q_gemm_mxfp8_blocked(const void* A, const void* SFA_blocked, const void* B, const void* SFB_blocked, void* C,
+                             int M, int N, int K, void* stream);
+int b200q_mxfp8_swizzle_sf(const void* sf_rowmajor, void* sf_blocked, int rows, int K, void* stream);
+size_t b200q_mxfp8_sf_bytes(int rows, int K);
+int b200q_mxfp8_set_tile_n(int bn);     /* width of the B tile of the MXFP8 GEMM: 256 (default) or 192 */
+
 /* 2:4 structured-sparse FP8 GEMM: C(bf16) = (expand(Acomp, Ameta) * B^T) * (scale_a * scale_b).
  * Acomp[M,K/2] E4M3 keeps the two retained values of every four in order; Ameta[M,K/8]: one
  * nibble per group of four = two ascending 2-bit positions, lower position in bits [1:0],

@@ -289,6 +289,34 @@ def dequant_nvfp4(q, sf, g: float) -> np.ndarray:
     return out
 
 
+def quant_mxfp8(x: np.ndarray):
+    """fp32 [rows, K] -> (E4M3 bytes [rows, K], UE8M0 scales [rows, K/32])."""
+    x = _c(x, np.float32)
+    R, Cc = x.shape
+    assert Cc % 32 == 0
+    q = np.empty((R, Cc), np.uint8); sf = np.empty((R, Cc // 32), np.uint8)
+    fn = lib().oracle_quant_mxfp8
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 3 + [C.c_int] * 2
+    fn(_p(x), _p(q), _p(sf), R, Cc)
+    return q, sf
+
+
+def dequant_mxfp8(q, sf) -> np.ndarray:
+    q = _c(q, np.uint8); sf = _c(sf, np.uint8)
+    R, Cc = q.shape
+    out = np.empty((R, Cc), np.float32)
+    fn = lib().oracle_dequant_mxfp8
+    fn.restype = None
+    fn.argtypes = [C.c_void_p] * 3 + [C.c_int] * 2
+    fn(_p(q), _p(sf), _p(out), R, Cc)
+    return out
+
+
+def decode_ue8m0(q: np.ndarray) -> np.ndarray:
+    return _lut("oracle_decode_ue8m0")[np.asarray(q, np.uint8)]
+
+
 def dequant_w4(wq, s_f16, group: int = 128) -> np.ndarray:
     wq = _c(wq, np.uint8); s = _c(s_f16, np.uint16)
     N, K2 = wq.shape
@@ -425,6 +453,20 @@ def make_nvfp4_case(M, N, K, seed=0):
     aq, sfa, ga = make_nvfp4_operand(M, K, rng)
     bq, sfb, gb = make_nvfp4_operand(N, K, rng)
     return aq, sfa, ga, bq, sfb, gb
+
+
+def make_mxfp8_case(M, N, K, seed=0, spread: bool = True):
+    """N(0,1) operands (rows scaled by 2^U(-6,6) when ``spread``, so the block scales differ) quantised to MXFP8."""
+    rng = np.random.default_rng(seed)
+
+    def operand(R):
+        x = rng.standard_normal((R, K), dtype=np.float32)
+        if spread:
+            x *= np.exp2(rng.integers(-6, 7, size=(R, K // 32))).astype(np.float32).repeat(32, axis=1)
+        return quant_mxfp8(x)
+    aq, sfa = operand(M)
+    bq, sfb = operand(N)
+    return aq, sfa, bq, sfb
 
 
 def make_sparse_fp8_case(M, N, K, seed=0):

@@ -354,6 +354,41 @@ void oracle_dequant_nvfp4(const uint8_t* q, const uint8_t* sf, float* out, int r
         }
 }
 
+/* MXFP8 quantisation of x[rows, cols]: per 32 contiguous K one UE8M0 scale 2^(e - 127) with
+ * e - 127 = floor(log2(max|blk|)) - 8 (8 = exponent of the largest E4M3 binade, so the block maximum lands
+ * in [256, 512) and saturates to 448 at most), q = e4m3_rn_satfinite(x / scale); an all-zero block gets scale
+ * byte 127 (1.0).  The format (E4M3 data, one UE8M0 per 32 K) is that of the reference's
+ * kind::mxf8f6f4.block_scale.scale_vec::1X test (op/test/arch_primitives/ptx_mma_fp8.cu:126-178); the rule for
+ * choosing the exponent is the usual microscaling one, the reference has none. */
+void oracle_quant_mxfp8(const float* x, uint8_t* q, uint8_t* sf, int rows, int cols)
+{
+    for (int r = 0; r < rows; ++r)
+        for (int b = 0; b < cols / 32; ++b) {
+            const float* xb = x + (size_t)r * cols + 32 * b;
+            float mx = 0.0f;
+            for (int t = 0; t < 32; ++t) mx = fmaxf(mx, fabsf(xb[t]));
+            int e = 127;
+            if (mx > 0.0f) {
+                int ex; frexpf(mx, &ex);                 /* mx = f * 2^ex, f in [0.5, 1): floor(log2 mx) = ex - 1 */
+                e = (ex - 1) - 8 + 127;
+                if (e < 0) e = 0;
+                if (e > 254) e = 254;
+            }
+            sf[(size_t)r * (cols / 32) + b] = (uint8_t)e;
+            const float inv = ldexpf(1.0f, 127 - e);     /* exact power of two */
+            for (int t = 0; t < 32; ++t) q[(size_t)r * cols + 32 * b + t] = oracle_encode_e4m3(xb[t] * inv);
+        }
+}
+
+/* MXFP8 -> fp32: value = e4m3 * 2^(sf - 127), one scale per 32 K
+ * (decoder: op/test/arch_primitives/ptx_mma_fp6.cu:344-351). */
+void oracle_dequant_mxfp8(const uint8_t* q, const uint8_t* sf, float* out, int rows, int cols)
+{
+    for (int r = 0; r < rows; ++r)
+        for (int c = 0; c < cols; ++c)
+            out[(size_t)r * cols + c] = oracle_decode_e4m3(q[(size_t)r * cols + c]) * oracle_decode_ue8m0(sf[(size_t)r * (cols / 32) + c / 32]);
+}
+
 /* W4A16 weights -> fp32: w[n,k] = q[n,k] * fp16 scale[n, k/group]; no zero point. */
 void oracle_dequant_w4(const uint8_t* wq, const uint16_t* s, float* out, int N, int K, int group)
 {
