@@ -21,8 +21,8 @@ LIB_PATH = os.path.join(_HERE, "libb200q.so")
 _lib = None
 
 __all__ = [
-    "lib", "gemm_fp8", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "gemm_nvfp4", "nvfp4_swizzle_sf",
-    "gemm_mxfp8", "mxfp8_swizzle_sf",
+    "lib", "gemm_fp8", "gemm_i8", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "gemm_nvfp4", "nvfp4_swizzle_sf",
+    "gemm_mxfp8", "mxfp8_swizzle_sf", "quant_rows_nvfp4",
     "gemm_sparse_fp8", "quant_rows_e4m3", "status", "check_status", "set_wait_limit_ms", "WaitTimeout", "LIB_PATH",
 ]
 
@@ -40,6 +40,7 @@ _SIZE_T_FUNCS = {
 }
 _SIGNATURES = {
     "b200q_gemm_fp8": [_VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
+    "b200q_gemm_i8": [_VP, _VP, _VP, _VP, _I, _I, _I, _VP],
     "b200q_gemm_fp8_rowcol": [_VP, _VP, _VP, _I, _I, _I, _VP, _VP, _I, _VP],
     "b200q_gemm_fp8_swiglu": [_VP, _VP, _VP, _VP, _I, _I, _I, _VP, _VP, _VP, _VP],
     "b200q_gemm_w4a16": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP],
@@ -62,6 +63,7 @@ _SIGNATURES = {
     "b200q_sp24_set_tile_n": [_I],
     "b200q_gemm_sp24_fp8": [_VP, _VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
     "b200q_quant_rows_e4m3": [_VP, _VP, _VP, _I, _I, _VP],
+    "b200q_quant_rows_nvfp4": [_VP, _VP, _VP, _I, _I, _F, _VP],
     "b200q_status": [_VP, _I],
     "b200q_set_wait_limit_ms": [_I, _I],
     "b200q_rank_barrier": [_VP, _I, _I, C.c_uint, C.c_uint, _VP],
@@ -125,7 +127,7 @@ def _check(t: torch.Tensor, name: str, dtypes, ndim: int) -> None:
 # signatures with defaults, as op/grouped_gemm/cudaop_grouped_gemm/ops.py does for its _C module.
 
 EXTENSION_OPS = ("gemm_fp8", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "nvfp4_swizzle_sf", "gemm_nvfp4",
-                 "mxfp8_swizzle_sf", "gemm_mxfp8", "gemm_sparse_fp8", "quant_rows_e4m3")
+                 "mxfp8_swizzle_sf", "gemm_mxfp8", "gemm_sparse_fp8", "quant_rows_e4m3", "quant_rows_nvfp4", "gemm_i8")
 try:
     from . import _C                                    # noqa: F401
     _C_ERROR = None
@@ -143,6 +145,11 @@ def _ext():
 def gemm_fp8(a: torch.Tensor, b: torch.Tensor, scale_a: float, scale_b: float) -> torch.Tensor:
     """C[M,N] (bf16) = (A[M,K] @ B[N,K].T) * (scale_a * scale_b); A, B hold E4M3 bytes."""
     return _ext().gemm_fp8(a, b, float(scale_a), float(scale_b))
+
+
+def gemm_i8(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None) -> torch.Tensor:
+    """D[M,N] (int32) = A[M,K] (int8) @ B[N,K].T (int8) (+ C int32): exact integer GEMM on the tensor cores."""
+    return _ext().gemm_i8(a, b, c)
 
 
 def gemm_fp8_rowcol(a, b, row_scale, col_scale, out_dtype=torch.bfloat16) -> torch.Tensor:
@@ -195,6 +202,12 @@ def gemm_sparse_fp8(a_comp, a_meta, b, scale_a: float, scale_b: float) -> torch.
 def quant_rows_e4m3(x: torch.Tensor):
     """bf16 [rows, cols] -> (E4M3 bytes [rows, cols] as uint8, fp32 scales [rows])."""
     return _ext().quant_rows_e4m3(x)
+
+
+def quant_rows_nvfp4(x: torch.Tensor, global_scale: float):
+    """bf16 [rows, cols] -> (packed E2M1 [rows, cols/2] uint8, UE4M3 scales in the blocked layout, 1-D uint8):
+    operands for :func:`gemm_nvfp4` with ``blocked=True``."""
+    return _ext().quant_rows_nvfp4(x, float(global_scale))
 
 
 def status(clear: bool = True) -> int:

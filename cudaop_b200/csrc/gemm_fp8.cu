@@ -109,9 +109,10 @@ struct ArArgs {
 
 cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int epi, int out_f32, float alpha,
                  const float* row_scale, const float* col_scale, const void* B2, const float* col_scale2,
-                 long long ldc, const ArArgs* ar, cudaStream_t stream)
+                 long long ldc, const ArArgs* ar, cudaStream_t stream, const int32_t* c_in = nullptr)
 {
     if (bad_operands(A, B, C, M, N, K)) return cudaErrorInvalidValue;
+    if (epi == kEpiInt32 && (!out_f32 || ar != nullptr)) return cudaErrorInvalidValue;      // 32-bit output words
     if (epi == kEpiRowCol && (row_scale == nullptr || col_scale == nullptr)) return cudaErrorInvalidValue;
     if (epi == kEpiSwiGLU &&
         (row_scale == nullptr || col_scale == nullptr || col_scale2 == nullptr || B2 == nullptr || !aligned16(B2)))
@@ -123,7 +124,7 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
     const int out_cols = swiglu ? bn / 2 : bn;
     Params p{};
     p.M = M; p.N = N; p.K = K; p.C = C; p.ldc = ldc; p.alpha = alpha;
-    p.row_scale = row_scale; p.col_scale = col_scale; p.col_scale2 = col_scale2;
+    p.row_scale = row_scale; p.col_scale = col_scale; p.col_scale2 = col_scale2; p.c_in = c_in;
     p.tiles_m = (M + kBM - 1) / kBM;
     p.tiles_n = (N + out_cols - 1) / out_cols;
     p.group = 16;
@@ -187,6 +188,7 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
         case kEpiTensor: return out_f32 ? B200Q_PAIR(kEpiTensor, float) : B200Q_PAIR(kEpiTensor, __nv_bfloat16);
         case kEpiRowCol: return out_f32 ? B200Q_PAIR(kEpiRowCol, float) : B200Q_PAIR(kEpiRowCol, __nv_bfloat16);
         case kEpiSwiGLU: return out_f32 ? cudaErrorInvalidValue : B200Q_PAIR(kEpiSwiGLU, __nv_bfloat16);
+        case kEpiInt32: return B200Q_PAIR(kEpiInt32, float);        // int32 words travel as 32-bit floats' bits
         default: return cudaErrorInvalidValue;
         }
 #undef B200Q_PAIR
@@ -210,6 +212,7 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
     case kEpiSwiGLU:
         if (out_f32) return cudaErrorInvalidValue;
         return B200Q_LAUNCH(kEpiSwiGLU, __nv_bfloat16, false);
+    case kEpiInt32: return B200Q_LAUNCH(kEpiInt32, float, false);
     default: return cudaErrorInvalidValue;
     }
 #undef B200Q_LAUNCH
@@ -225,6 +228,13 @@ int b200q_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K, f
 {
     return b200q::fp8::gemm(A, B, C, M, N, K, b200q::fp8::kEpiTensor, 0, scale_a * scale_b, nullptr, nullptr,
                             nullptr, nullptr, N, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_gemm_i8(const void* A, const void* B, const void* C_in, void* D, int M, int N, int K, void* stream)
+{
+    if (D == C_in && D != nullptr) { /* in place is fine: every element is read and written by the same thread */ }
+    return b200q::fp8::gemm(A, B, D, M, N, K, b200q::fp8::kEpiInt32, 1, 1.0f, nullptr, nullptr, nullptr, nullptr, N, nullptr,
+                            static_cast<cudaStream_t>(stream), static_cast<const int32_t*>(C_in));
 }
 
 int b200q_gemm_fp8_rowcol(const void* A, const void* B, void* C, int M, int N, int K, const float* row_scale,

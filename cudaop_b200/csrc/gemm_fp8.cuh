@@ -55,6 +55,7 @@ enum Epilogue : int {
     kEpiTensor = 0,   // C = acc * alpha                                  (per-tensor scales)
     kEpiRowCol = 1,   // C = acc * (row_scale[m] * col_scale[n])          (per-token x per-channel)
     kEpiSwiGLU = 2,   // B tile = BN/2 gate rows + BN/2 up rows; C[m,n] = silu(g) * u, BN/2 columns per tile
+    kEpiInt32 = 3,    // signed 8-bit operands (kind::i8), C(int32) = acc (+ c_in): exact integer GEMM
 };
 
 struct Params {
@@ -65,6 +66,7 @@ struct Params {
     const float* row_scale;      // [M]
     const float* col_scale;      // [N]   (gate scales for SwiGLU)
     const float* col_scale2;     // [N]   (up scales for SwiGLU)
+    const int32_t* c_in;         // [M, ldc] int32 added to the integer accumulator, or nullptr (kEpiInt32)
     int tiles_m, tiles_n;
     int group;                   // tile rows that walk the N tiles together
     uint32_t* status;
@@ -215,7 +217,7 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* tmA, const CUte
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
         if (ptx::elect_one()) {
-            constexpr uint32_t idesc = ptx::umma_idesc(0 /*E4M3*/, 0 /*E4M3*/, kBM, BN);
+            constexpr uint32_t idesc = (EPI == kEpiInt32) ? ptx::umma_idesc_i8(kBM, BN) : ptx::umma_idesc(0 /*E4M3*/, 0 /*E4M3*/, kBM, BN);
             int stage = 0; uint32_t phase = 0; bool ok = true;
             int t = 0;
             for (int tile = cta; tile < num_tiles && ok; tile += nctas, ++t) {
@@ -229,8 +231,10 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* tmA, const CUte
                     const uint32_t sa = smem_base + stage * kStageBytes, sb = sa + CF::kABytes;
                     const uint64_t da = ptx::smem_desc_sw128_kmajor(sa), db = ptx::smem_desc_sw128_kmajor(sb);
 #pragma unroll
-                    for (int k = 0; k < kBK / 32; ++k)   // 32 bytes of K per instruction: +2 in 16-byte units
-                        ptx::umma_f8f6f4(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < kBK / 32; ++k) {  // 32 bytes of K per instruction: +2 in 16-byte units
+                        if (EPI == kEpiInt32) ptx::umma_i8(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0);
+                        else ptx::umma_f8f6f4(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0);
+                    }
                     ptx::umma_commit(empty_bar(stage));
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
@@ -253,7 +257,7 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* tmA, const CUte
             ptx::tcgen05_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 256;
             float rs = 1.0f;
-            if (EPI != kEpiTensor) rs = (row < p.M) ? __ldg(p.row_scale + row) : 0.0f;
+            if (EPI == kEpiRowCol || EPI == kEpiSwiGLU) rs = (row < p.M) ? __ldg(p.row_scale + row) : 0.0f;
 #pragma unroll 1
             for (int c = 0; c < kOutCols / kCW; ++c) {
                 uint32_t r[kCW];
@@ -272,6 +276,16 @@ __device__ __forceinline__ void gemm_fp8_body(const CUtensorMap* tmA, const CUte
                         const float g = __uint_as_float(r[i]) * (rs * sg);
                         const float u = __uint_as_float(ru[i]) * (rs * su);
                         v[i] = g / (1.0f + __expf(-g)) * u;
+                    }
+                } else if (EPI == kEpiInt32) {
+                    // the accumulator is a 32-bit integer: pass its bits through (plus the optional addend, wrapping)
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < kCW; ++i) {
+                        uint32_t acc = r[i];
+                        if (p.c_in != nullptr && row < p.M && col0 + i < p.N)
+                            acc += static_cast<uint32_t>(__ldg(p.c_in + (long long)row * p.ldc + col0 + i));
+                        v[i] = __uint_as_float(acc);
                     }
                 } else {
                     ptx::tmem_ld_wait();

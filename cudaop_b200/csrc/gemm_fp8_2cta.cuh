@@ -110,7 +110,7 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer (leader CTA only)
         if (cta_rank == 0 && ptx::elect_one()) {
-            constexpr uint32_t idesc = ptx::umma_idesc(0, 0, kPairBM, kPairBN);
+            constexpr uint32_t idesc = (EPI == kEpiInt32) ? ptx::umma_idesc_i8(kPairBM, kPairBN) : ptx::umma_idesc(0, 0, kPairBM, kPairBN);
             int stage = 0; uint32_t phase = 0; bool ok = true;
             int t = 0;
             for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
@@ -124,8 +124,10 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     const uint32_t sa = smem_base + stage * kPairStageBytes, sb = sa + kBM * kBK;
                     const uint64_t da = ptx::smem_desc_sw128_kmajor(sa), db = ptx::smem_desc_sw128_kmajor(sb);
 #pragma unroll
-                    for (int k = 0; k < kBK / 32; ++k)
-                        ptx::umma_f8f6f4_2cta(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < kBK / 32; ++k) {
+                        if (EPI == kEpiInt32) ptx::umma_i8_2cta(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0);
+                        else ptx::umma_f8f6f4_2cta(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0);
+                    }
                     ptx::umma_commit_2cta(empty_bar(stage), 3);        // slot free on both CTAs
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
@@ -156,7 +158,7 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             ptx::tcgen05_fence_after_sync();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 256;
             float rs = 1.0f;
-            if (EPI != kEpiTensor) rs = (row < p.M) ? __ldg(p.row_scale + row) : 0.0f;
+            if (EPI == kEpiRowCol || EPI == kEpiSwiGLU) rs = (row < p.M) ? __ldg(p.row_scale + row) : 0.0f;
 #pragma unroll 1
             for (int c = 0; c < kOutCols / kCW; ++c) {
                 uint32_t r[kCW];
@@ -175,6 +177,16 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                         const float g = __uint_as_float(r[i]) * (rs * sg);
                         const float u = __uint_as_float(ru[i]) * (rs * su);
                         v[i] = g / (1.0f + __expf(-g)) * u;
+                    }
+                } else if (EPI == kEpiInt32) {
+                    // the accumulator is a 32-bit integer: pass its bits through (plus the optional addend, wrapping)
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < kCW; ++i) {
+                        uint32_t acc = r[i];
+                        if (p.c_in != nullptr && row < p.M && col0 + i < p.N)
+                            acc += static_cast<uint32_t>(__ldg(p.c_in + (long long)row * p.ldc + col0 + i));
+                        v[i] = __uint_as_float(acc);
                     }
                 } else {
                     ptx::tmem_ld_wait();

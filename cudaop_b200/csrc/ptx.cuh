@@ -285,6 +285,13 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, uint32_t b_fmt
            ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
+// Instruction descriptor, kind::i8: signed 8-bit operands (format 1; 0 = unsigned), 32-bit integer accumulator
+// (D format 2), both operands K-major, no saturation.
+__host__ __device__ constexpr uint32_t umma_idesc_i8(uint32_t m, uint32_t n)
+{
+    return (2u << 4) /* D = s32 */ | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
 // Instruction descriptor for block-scaled kinds (mxf8f6f4 / mxf4nvf4): no D-format
 // field (always f32); scale-factor ids select a byte column inside the 32-bit TMEM
 // scale column; scale format 0 = UE4M3, 1 = UE8M0.
@@ -317,6 +324,28 @@ __device__ __forceinline__ void umma_f8f6f4_2cta(uint32_t d_tmem, uint64_t a_des
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// tcgen05.mma.cta_group::1.kind::i8: 8-bit integer operands (signedness per operand in idesc), 32-bit integer
+// accumulation in TMEM (exact, wrapping)
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// tcgen05.mma.cta_group::2.kind::i8 (issued by the leader CTA of a pair)
+__device__ __forceinline__ void umma_i8_2cta(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }

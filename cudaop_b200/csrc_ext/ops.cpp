@@ -73,6 +73,23 @@ torch::Tensor gemm_fp8(torch::Tensor a, torch::Tensor b, double scale_a, double 
     return c;
 }
 
+torch::Tensor gemm_i8(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> c)
+{
+    check_cuda_2d(a, "a", {kI8}); check_cuda_2d(b, "b", {kI8}); same_device({&a, &b});
+    TORCH_CHECK_VALUE(a.size(1) == b.size(1), "inner dimensions differ: ", a.size(1), " vs ", b.size(1));
+    const void* cin = nullptr;
+    if (c.has_value()) {
+        check_cuda_2d(*c, "c", {kI32}); same_device({&a, &*c});
+        TORCH_CHECK_VALUE(c->size(0) == a.size(0) && c->size(1) == b.size(0), "c must be [M, N]");
+        cin = c->data_ptr();
+    }
+    const c10::cuda::CUDAGuard guard(a.device());
+    auto d = out_like(a, {a.size(0), b.size(0)}, kI32);
+    raise_on(b200q_gemm_i8(a.data_ptr(), b.data_ptr(), cin, d.data_ptr(), (int)a.size(0), (int)b.size(0), (int)a.size(1), stream_of(a)),
+             "b200q_gemm_i8");
+    return d;
+}
+
 torch::Tensor gemm_fp8_rowcol(torch::Tensor a, torch::Tensor b, torch::Tensor row_scale, torch::Tensor col_scale, bool out_f32)
 {
     check_cuda_2d(a, "a", {kU8, kE4M3}); check_cuda_2d(b, "b", {kU8, kE4M3});
@@ -214,9 +231,23 @@ std::tuple<torch::Tensor, torch::Tensor> quant_rows_e4m3(torch::Tensor x)
     return {q, s};
 }
 
+std::tuple<torch::Tensor, torch::Tensor> quant_rows_nvfp4(torch::Tensor x, double global_scale)
+{
+    check_cuda_2d(x, "x", {kBF16});
+    TORCH_CHECK_VALUE(x.size(1) % 64 == 0, "the row length must be a multiple of 64");
+    TORCH_CHECK_VALUE(global_scale > 0.0, "global_scale must be positive");
+    const c10::cuda::CUDAGuard guard(x.device());
+    auto q = out_like(x, {x.size(0), x.size(1) / 2}, kU8);
+    auto sf = out_like(x, {(int64_t)b200q_nvfp4_sf_bytes((int)x.size(0), (int)x.size(1))}, kU8);
+    raise_on(b200q_quant_rows_nvfp4(x.data_ptr(), q.data_ptr(), sf.data_ptr(), (int)x.size(0), (int)x.size(1), (float)global_scale,
+                                    stream_of(x)), "b200q_quant_rows_nvfp4");
+    return {q, sf};
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
 {
     m.def("gemm_fp8", &gemm_fp8, "FP8 E4M3 GEMM, per-tensor scales, bf16 out");
+    m.def("gemm_i8", &gemm_i8, "exact INT8 GEMM with int32 accumulation", pybind11::arg("a"), pybind11::arg("b"), pybind11::arg("c") = pybind11::none());
     m.def("gemm_fp8_rowcol", &gemm_fp8_rowcol, "FP8 E4M3 GEMM, per-row x per-column scales");
     m.def("gemm_fp8_swiglu", &gemm_fp8_swiglu, "fused gate/up projection + SwiGLU on FP8 operands");
     m.def("gemm_w4a16", &gemm_w4a16, "INT4 weight-only GEMM, bf16 activations");
@@ -226,6 +257,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
     m.def("gemm_mxfp8", &gemm_mxfp8, "MXFP8 block-scaled GEMM");
     m.def("gemm_sparse_fp8", &gemm_sparse_fp8, "2:4-sparse FP8 GEMM");
     m.def("quant_rows_e4m3", &quant_rows_e4m3, "bf16 rows -> E4M3 + per-row fp32 scale");
+    m.def("quant_rows_nvfp4", &quant_rows_nvfp4, "bf16 rows -> packed E2M1 + blocked UE4M3 scales");
 }
 
 }  // namespace cudaop_b200

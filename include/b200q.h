@@ -33,6 +33,13 @@ extern "C" {
 int b200q_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K,
                    float scale_a, float scale_b, void* stream);
 
+/* INT8 GEMM, exact: D[M,N](int32) = A[M,K](s8) * B[N,K](s8)^T + C_in[M,N](int32, or NULL for none), 32-bit wrapping
+ * integer arithmetic on the tensor cores (tcgen05 kind::i8).  The S8 case of the reference's integer MMA test as a
+ * whole GEMM: signed bytes in two's complement, D = A*B + C with an int32 accumulator
+ * (op/test/arch_primitives/ptx_mma_integer.cu:72-92 byte packing, :387-401 reference value).  C_in may equal D.
+ * Requires K % 16 == 0 and 16-byte aligned A, B. */
+int b200q_gemm_i8(const void* A, const void* B, const void* C_in, void* D, int M, int N, int K, void* stream);
+
 /* Same contraction with per-row and per-column fp32 scales (device arrays):
  * C[m,n] = acc * (row_scale[m] * col_scale[n]); out_f32 != 0 writes fp32 instead of bf16.
  * This is the down projection of the tensor-parallel MLP (row-parallel second GEMM of
@@ -147,6 +154,14 @@ int b200q_sp24_set_2cta(int on);       /* 2:4-sparse GEMM on CTA pairs (256 x 22
  * S[r] = max(max|X[r,:]| / 448, 2^-126) (1 for a zero row), Q = rn_satfinite(X * (1 / S[r])).  No counterpart in
  * the reference (its MLP is fp32); needed on either side of the FP8 GEMMs.  cols % 8 == 0. */
 int b200q_quant_rows_e4m3(const void* X, void* Q, float* S, int rows, int cols, void* stream);
+
+/* Activation quantiser to NVFP4: X[rows,cols] bf16 -> Q[rows,cols/2] (two E2M1 per byte, low nibble = lower K) and
+ * one UE4M3 scale per 16 K written directly in the blocked layout of b200q_gemm_nvfp4_blocked
+ * (b200q_nvfp4_sf_bytes(rows, cols) bytes; the rows that pad the last 128-row block get zero scales).
+ * sf = ue4m3_rn((max|block| / 6) / global_scale), q = e2m1_rn(x * (1 / (decode(sf) * global_scale))).  Formats:
+ * op/test/arch_primitives/ptx_mma_fp4.cu:55-65,120-144,293-309; the reference has no quantiser.  cols % 64 == 0,
+ * global_scale > 0 (normally max|X| / (6 * 448)); X, SF 16-byte aligned, Q 4-byte aligned. */
+int b200q_quant_rows_nvfp4(const void* X, void* Q, void* SF_blocked, int rows, int cols, float global_scale, void* stream);
 
 /* Sum all-reduce of the MLP's fp32 partial outputs over NVLink / NVSwitch, one call per rank, all
  * ranks at the same time: Y(bf16, on every rank) = sum_r P_r, P_r fp32 or (partial_is_bf16) bf16.  Replaces the in-place

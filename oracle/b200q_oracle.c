@@ -323,9 +323,12 @@ void oracle_quant_rows_e4m3(const float* x, uint8_t* q, float* s, int rows, int 
 }
 
 /* NVFP4 quantisation of x[rows, cols] with a given global scale g:
- * per 16 contiguous K: sf = ue4m3_rn((max|blk| / 6) / g), q = e2m1_rn(x / (sf_decoded * g)),
- * two E2M1 per byte, low nibble first; sf laid out row-major [rows, cols/16].
- * Scale rule: one UE4M3 per 16 consecutive K (op/test/arch_primitives/ptx_mma_fp4.cu:55-65). */
+ * per 16 contiguous K: sf = ue4m3_rn((max|blk| / 6) / g), d = sf_decoded * g, q = e2m1_rn(x * (1 / d)) — one fp32
+ * reciprocal per block and one fp32 product per element, each rounded to nearest, then the E2M1 rounding (ties to
+ * the even code); a block whose d is below the smallest normal float (all zeros, or a vanishing g) is all zeros.
+ * Two E2M1 per byte, low nibble first; sf laid out row-major [rows, cols/16].
+ * Scale rule: one UE4M3 per 16 consecutive K (op/test/arch_primitives/ptx_mma_fp4.cu:55-65); the reference has no
+ * quantiser, the rule is stated here and the GPU quantiser reproduces it bit for bit. */
 void oracle_quant_nvfp4(const float* x, uint8_t* q, uint8_t* sf, int rows, int cols, float g)
 {
     for (int r = 0; r < rows; ++r)
@@ -333,11 +336,18 @@ void oracle_quant_nvfp4(const float* x, uint8_t* q, uint8_t* sf, int rows, int c
             const float* xb = x + (size_t)r * cols + 16 * b;
             float mx = 0.0f;
             for (int t = 0; t < 16; ++t) mx = fmaxf(mx, fabsf(xb[t]));
-            uint8_t s8 = oracle_encode_ue4m3((mx / 6.0f) / g);
+            volatile float t6 = mx / 6.0f;
+            volatile float tg = t6 / g;
+            uint8_t s8 = oracle_encode_ue4m3(tg);
             sf[(size_t)r * (cols / 16) + b] = s8;
-            float d = oracle_decode_ue4m3(s8) * g;
+            volatile float d = oracle_decode_ue4m3(s8) * g;
+            const int live = d >= 1.17549435e-38f;
+            volatile float inv = live ? 1.0f / d : 0.0f;
             uint8_t nib[16];
-            for (int t = 0; t < 16; ++t) nib[t] = d > 0.0f ? oracle_encode_e2m1(xb[t] / d) : 0;
+            for (int t = 0; t < 16; ++t) {
+                volatile float y = xb[t] * inv;
+                nib[t] = live ? oracle_encode_e2m1(y) : 0;
+            }
             oracle_pack_u4(nib, q + ((size_t)r * cols + 16 * b) / 2, 16);
         }
 }
