@@ -21,7 +21,7 @@ LIB_PATH = os.path.join(_HERE, "libb200q.so")
 _lib = None
 
 __all__ = [
-    "lib", "gemm_fp8", "gemm_i8", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "gemm_nvfp4", "nvfp4_swizzle_sf",
+    "lib", "gemm_fp8", "gemm_i8", "gmm", "gmm_fp8", "GroupedFP8Weights", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "gemm_nvfp4", "nvfp4_swizzle_sf",
     "gemm_mxfp8", "mxfp8_swizzle_sf", "quant_rows_nvfp4",
     "gemm_sparse_fp8", "quant_rows_e4m3", "status", "check_status", "set_wait_limit_ms", "WaitTimeout", "LIB_PATH",
 ]
@@ -41,6 +41,7 @@ _SIZE_T_FUNCS = {
 _SIGNATURES = {
     "b200q_gemm_fp8": [_VP, _VP, _VP, _I, _I, _I, _F, _F, _VP],
     "b200q_gemm_i8": [_VP, _VP, _VP, _VP, _I, _I, _I, _VP],
+    "b200q_gmm_fp8": [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP],
     "b200q_gemm_fp8_rowcol": [_VP, _VP, _VP, _I, _I, _I, _VP, _VP, _I, _VP],
     "b200q_gemm_fp8_swiglu": [_VP, _VP, _VP, _VP, _I, _I, _I, _VP, _VP, _VP, _VP],
     "b200q_gemm_w4a16": [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP],
@@ -127,7 +128,7 @@ def _check(t: torch.Tensor, name: str, dtypes, ndim: int) -> None:
 # signatures with defaults, as op/grouped_gemm/cudaop_grouped_gemm/ops.py does for its _C module.
 
 EXTENSION_OPS = ("gemm_fp8", "gemm_fp8_rowcol", "gemm_fp8_swiglu", "gemm_w4a16", "nvfp4_swizzle_sf", "gemm_nvfp4",
-                 "mxfp8_swizzle_sf", "gemm_mxfp8", "gemm_sparse_fp8", "quant_rows_e4m3", "quant_rows_nvfp4", "gemm_i8")
+                 "mxfp8_swizzle_sf", "gemm_mxfp8", "gemm_sparse_fp8", "quant_rows_e4m3", "quant_rows_nvfp4", "gemm_i8", "gmm_fp8")
 try:
     from . import _C                                    # noqa: F401
     _C_ERROR = None
@@ -150,6 +151,40 @@ def gemm_fp8(a: torch.Tensor, b: torch.Tensor, scale_a: float, scale_b: float) -
 def gemm_i8(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor | None = None) -> torch.Tensor:
     """D[M,N] (int32) = A[M,K] (int8) @ B[N,K].T (int8) (+ C int32): exact integer GEMM on the tensor cores."""
     return _ext().gemm_i8(a, b, c)
+
+
+def gmm_fp8(a_q, a_scale, b_q, b_scale, batch_sizes) -> torch.Tensor:
+    """Grouped GEMM on quantised operands: a_q [tokens, K] E4M3 with per-token scales [tokens]; b_q [E, N, K] E4M3 with
+    per-channel scales [E, N]; batch_sizes [E] int64 (CPU or CUDA): rows per group.  Returns [tokens, N] bf16; rows not
+    covered by any group are zero."""
+    return _ext().gmm_fp8(a_q, a_scale, b_q, b_scale, batch_sizes)
+
+
+class GroupedFP8Weights:
+    """Expert weights quantised once for :func:`gmm`: E4M3 bytes [E, N, K] (K contiguous) + fp32 scales [E, N],
+    one per expert and output channel (max |w| / 448 over K)."""
+
+    def __init__(self, b: torch.Tensor, trans_b: bool = False):
+        if b.dim() != 3 or b.dtype != torch.bfloat16 or not b.is_cuda:
+            raise ValueError("b must be a CUDA bf16 tensor [E, K, N] (trans_b=False) or [E, N, K] (trans_b=True)")
+        w = b if trans_b else b.transpose(1, 2)
+        w = w.contiguous()                                   # [E, N, K]
+        E, N, K = w.shape
+        q, s = quant_rows_e4m3(w.view(E * N, K))
+        self.q, self.scale = q.view(E, N, K), s.view(E, N)
+        self.E, self.N, self.K = E, N, K
+
+
+def gmm(a: torch.Tensor, b, batch_sizes: torch.Tensor, trans_b: bool = False) -> torch.Tensor:
+    """The reference's ``gmm(a, b, batch_sizes, trans_b)`` (op/grouped_gemm/cudaop_grouped_gemm/ops.py:76-83) on the
+    FP8 tensor cores: ``a`` [tokens, K] bf16 is split into consecutive groups of ``batch_sizes[e]`` rows and group e
+    is multiplied by expert e's weights.  ``b`` is a :class:`GroupedFP8Weights` (quantise once, reuse) or the
+    reference's bf16 tensor — [E, K, N], or [E, N, K] with ``trans_b`` — which is then quantised on every call.
+    Activations are quantised per token (E4M3), weights per output channel; the result is bf16 [tokens, N].
+    Forward only (the reference's autograd wrapper has no quantised counterpart)."""
+    w = b if isinstance(b, GroupedFP8Weights) else GroupedFP8Weights(b, trans_b)
+    a_q, a_s = quant_rows_e4m3(a)
+    return gmm_fp8(a_q, a_s, w.q, w.scale, batch_sizes)
 
 
 def gemm_fp8_rowcol(a, b, row_scale, col_scale, out_dtype=torch.bfloat16) -> torch.Tensor:

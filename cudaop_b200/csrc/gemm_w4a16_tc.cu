@@ -341,7 +341,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
     }
 }
 
-int g_impl = 0;      // 0 = by M: CUDA-core GEMV (gemm_w4a16_gemv.cu) for one token, else the warp-MMA kernel (gemm_w4a16.cu);
+int g_impl = 0;      // 0 = by M: streaming GEMV (gemm_w4a16_stream.cu; the older GEMV forms of gemm_w4a16_gemv.cu when K does not suit it)
+                     // for one token, else the warp-MMA kernel (gemm_w4a16.cu); 5 = the same choice, named;
                      // 1 = tcgen05 kernel (this file); 2 = warp-MMA kernel for every M; 3 / 4 = GEMV up to 4 tokens, weights
                      // through shared memory (dp4a arithmetic) / in registers (fp32 arithmetic)
 int g_pdl = 0;       // programmatic dependent launch (b200q_w4a16_set_pdl) of the GEMV and tcgen05 kernels, off by default
@@ -356,11 +357,13 @@ namespace b200q {
 // gemm_w4a16_gemv.cu: CUDA-core kernel for M <= 4
 int gemm_w4a16_gemv(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, int pdl, int form,
                     void* stream);
+// gemm_w4a16_stream.cu: one token, fat CTAs that prefetch their whole weight block (K % 2048 == 0, K <= 16384)
+int gemm_w4a16_stream(const void* X, const void* Wq, const void* S, void* Y, int N, int K, int group, int pdl, void* stream);
 }
 
 extern "C" int b200q_w4a16_set_impl(int impl)
 {
-    if (impl < 0 || impl > 4) return cudaErrorInvalidValue;
+    if (impl < 0 || impl > 5) return cudaErrorInvalidValue;
     b200q::w4tc::g_impl = impl;
     return 0;
 }
@@ -375,7 +378,9 @@ extern "C" int b200q_gemm_w4a16(const void* X, const void* Wq, const void* S, vo
                                 void* stream)
 {
     using namespace b200q;
-    if (M == 1 && w4tc::g_impl == 0) {
+    if (M == 1 && (w4tc::g_impl == 0 || w4tc::g_impl == 5) && group == 128 && K > 0 && K % 2048 == 0 && K <= 16384)
+        return gemm_w4a16_stream(X, Wq, S, Y, N, K, group, w4tc::g_pdl, stream);
+    if (M == 1 && (w4tc::g_impl == 0 || w4tc::g_impl == 5)) {
         // one token: CUDA cores.  Measured (K = 4096, 80 weight sets cycled in a graph): up to 8 MiB of weights the
         // form with the weights in registers is ahead (4096 rows: 4.7 vs 5.1 us), beyond it the shared-memory /
         // dp4a form (8192 rows: 6.6 vs 8.4 us).

@@ -90,6 +90,25 @@ torch::Tensor gemm_i8(torch::Tensor a, torch::Tensor b, c10::optional<torch::Ten
     return d;
 }
 
+torch::Tensor gmm_fp8(torch::Tensor a, torch::Tensor a_scale, torch::Tensor b, torch::Tensor b_scale, torch::Tensor batch_sizes)
+{
+    check_cuda_2d(a, "a", {kU8, kE4M3}); check_cuda_2d(b, "b", {kU8, kE4M3}, 3);
+    check_cuda_2d(a_scale, "a_scale", {kF32}, 1); check_cuda_2d(b_scale, "b_scale", {kF32}, 2);
+    same_device({&a, &a_scale, &b, &b_scale});
+    const int64_t T = a.size(0), K = a.size(1), E = b.size(0), N = b.size(1);
+    TORCH_CHECK_VALUE(b.size(2) == K && a_scale.numel() == T && b_scale.size(0) == E && b_scale.size(1) == N, "shape mismatch");
+    TORCH_CHECK_VALUE(batch_sizes.dim() == 1 && batch_sizes.numel() == E && batch_sizes.scalar_type() == c10::ScalarType::Long,
+                      "batch_sizes must be a 1-D int64 tensor with one entry per expert");
+    const c10::cuda::CUDAGuard guard(a.device());
+    // the reference passes batch_sizes on the CPU (op/grouped_gemm/csrc/grouped_gemm.cuh:106-143); the kernel reads it on the device
+    auto bs = batch_sizes.is_cuda() ? batch_sizes.contiguous() : batch_sizes.to(a.device(), /*non_blocking=*/false).contiguous();
+    auto c = torch::zeros({T, N}, a.options().dtype(kBF16));
+    raise_on(b200q_gmm_fp8(a.data_ptr(), a_scale.data_ptr<float>(), b.data_ptr(), b_scale.data_ptr<float>(),
+                           reinterpret_cast<const long long*>(bs.data_ptr<int64_t>()), c.data_ptr(), (int)T, (int)N, (int)K, (int)E,
+                           stream_of(a)), "b200q_gmm_fp8");
+    return c;
+}
+
 torch::Tensor gemm_fp8_rowcol(torch::Tensor a, torch::Tensor b, torch::Tensor row_scale, torch::Tensor col_scale, bool out_f32)
 {
     check_cuda_2d(a, "a", {kU8, kE4M3}); check_cuda_2d(b, "b", {kU8, kE4M3});
@@ -248,6 +267,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m)
 {
     m.def("gemm_fp8", &gemm_fp8, "FP8 E4M3 GEMM, per-tensor scales, bf16 out");
     m.def("gemm_i8", &gemm_i8, "exact INT8 GEMM with int32 accumulation", pybind11::arg("a"), pybind11::arg("b"), pybind11::arg("c") = pybind11::none());
+    m.def("gmm_fp8", &gmm_fp8, "grouped (ragged-M) FP8 GEMM");
     m.def("gemm_fp8_rowcol", &gemm_fp8_rowcol, "FP8 E4M3 GEMM, per-row x per-column scales");
     m.def("gemm_fp8_swiglu", &gemm_fp8_swiglu, "fused gate/up projection + SwiGLU on FP8 operands");
     m.def("gemm_w4a16", &gemm_w4a16, "INT4 weight-only GEMM, bf16 activations");

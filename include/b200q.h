@@ -33,6 +33,16 @@ extern "C" {
 int b200q_gemm_fp8(const void* A, const void* B, void* C, int M, int N, int K,
                    float scale_a, float scale_b, void* stream);
 
+/* Grouped (ragged-M) FP8 GEMM: the rows of A[tokens,K] form E consecutive groups of batch_sizes[e] rows, group e is
+ * multiplied by its own B[e][N,K]:  C[t,n](bf16) = (A[t,:] . B[e(t)][n,:]) * a_scale[t] * b_scale[e(t)*N + n].
+ * The quantized counterpart of the reference's gmm(a, b, batch_sizes, trans_b = True)
+ * (op/grouped_gemm/cudaop_grouped_gemm/ops.py:76-83, op/grouped_gemm/csrc/grouped_gemm.cuh:96-328): one persistent
+ * launch, the tile -> group map is derived on the device from batch_sizes (DEVICE array of E int64; rows beyond
+ * `tokens` are ignored, rows not covered by any group are left untouched in C).  E <= 1024, K % 16 == 0, A and B
+ * 16-byte aligned. */
+int b200q_gmm_fp8(const void* A, const float* a_scale, const void* B, const float* b_scale, const long long* batch_sizes_dev,
+                  void* C, int tokens, int N, int K, int E, void* stream);
+
 /* INT8 GEMM, exact: D[M,N](int32) = A[M,K](s8) * B[N,K](s8)^T + C_in[M,N](int32, or NULL for none), 32-bit wrapping
  * integer arithmetic on the tensor cores (tcgen05 kind::i8).  The S8 case of the reference's integer MMA test as a
  * whole GEMM: signed bytes in two's complement, D = A*B + C with an int32 accumulator
@@ -141,7 +151,8 @@ int b200q_fp8_set_reducer_stride(int stride);   /* fused all-reduce: every strid
 int b200q_nvfp4_set_tile_n(int bn);
 int b200q_nvfp4_set_2cta(int on);      /* NVFP4 GEMM on CTA pairs (256 x 192 / 256 x 256 tiles per pair) when M > 128 and the
                                         * tile width is not 128; default on */
-int b200q_w4a16_set_impl(int impl);     /* 0 = by M (default): CUDA-core GEMV for one token, warp-MMA kernel above;
+int b200q_w4a16_set_impl(int impl);     /* 0 = by M (default): streaming CUDA-core GEMV for one token (the older GEMV forms when K is not
+                                         * a multiple of 2048 or exceeds 16384), warp-MMA kernel above;
                                          * 1 = tcgen05 kernel; 2 = warp-MMA kernel for every M; 3 / 4 = the two GEMV forms
                                          * (shared memory + dp4a / registers + fp32) for up to 4 tokens */
 int b200q_w4a16_set_pdl(int on);        /* programmatic dependent launch of the GEMV / tcgen05 W4A16 kernels (default off):

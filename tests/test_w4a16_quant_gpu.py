@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(params=[(0, 0), (3, 1), (4, 0), (1, 0), (2, 0)], ids=["by_m", "gemv_pdl", "gemv_regs", "tcgen05", "warp_mma"],
                 autouse=True)
 def impl(request):
-    """Every implementation behind b200q_gemm_w4a16: the default (CUDA-core GEMV for one token, warp-MMA
+    """Every implementation behind b200q_gemm_w4a16: the default (streaming CUDA-core GEMV for one token, warp-MMA
     kernel above), the GEMV for up to four tokens with programmatic dependent launch, its form with the
     weights in registers, the tcgen05 kernel, the warp-MMA kernel for every M."""
     import cudaop_b200 as ops
@@ -62,6 +62,40 @@ def test_ragged_shapes(shape):
     out = ops.gemm_w4a16(dev(xb, torch.bfloat16), dev(wq), dev(s, torch.float16))
     torch.cuda.synchronize()
     assert_bar(bf16_to_f32(out), _w4_ref(xb, wq, s), K, str(shape))
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (100, 2048), (1000, 8192), (4099, 4096), (37, 16384), (28672, 4096),
+                                   (8, 6144)])
+@pytest.mark.parametrize("pdl", [0, 1])
+def test_one_token_streaming_form(shape, pdl, impl):
+    """The streaming GEMV (whole weight block of a CTA prefetched by bulk copies, K a multiple of 2048 up to 16384):
+    ragged row counts, several CTAs per SM, scales loaded by copy or by threads, with and without programmatic
+    dependent launch, three calls in a row on different weights."""
+    import cudaop_b200 as ops
+    if impl != (0, 0):
+        pytest.skip("selects its own implementation")
+    N, K = shape
+    ops.lib().b200q_w4a16_set_impl(5)
+    ops.lib().b200q_w4a16_set_pdl(pdl)
+    cases = [oracle.make_w4a16_case(1, N, K, seed=N + K + i) for i in range(2 if N > 8000 else 3)]
+    devs = [(dev(xb, torch.bfloat16), dev(wq), dev(s, torch.float16)) for xb, wq, s in cases]
+    outs = [ops.gemm_w4a16(*d) for d in devs]              # back to back on one stream
+    torch.cuda.synchronize()
+    assert ops.status() == 0
+    for (xb, wq, s), out in zip(cases, outs):
+        assert_bar(bf16_to_f32(out), _w4_ref(xb, wq, s), K, f"stream {shape} pdl={pdl}")
+
+
+def test_one_token_streaming_form_propagates_non_finite_activations(impl):
+    import cudaop_b200 as ops
+    if impl != (0, 0):
+        pytest.skip("selects its own implementation")
+    xb, wq, s = oracle.make_w4a16_case(1, 64, 2048, seed=9)
+    x = oracle.decode_bf16(xb).copy(); x[0, 5] = np.inf
+    ops.lib().b200q_w4a16_set_impl(5)
+    out = ops.gemm_w4a16(dev(oracle.encode_bf16(x), torch.bfloat16), dev(wq), dev(s, torch.float16))
+    torch.cuda.synchronize()
+    assert torch.isnan(out.float()).all()                  # Inf * 0-weight terms make the reference NaN as well
 
 
 def test_w4a16_is_deterministic():
