@@ -460,6 +460,8 @@ def run_ours(args):
     if world != args.gpus and rank == 0:
         print(f"warning: --gpus {args.gpus} but WORLD_SIZE={world}", file=sys.stderr)
     ops.lib()   # fails loudly if the CUDA library is missing
+    if args.static_tiles:
+        ops.lib().b200q_fp8_set_dynamic_tiles(0)
     peaks = measured_peaks()
 
     # synthetic weights, generated shard by shard on the device from per-row seeds so that every
@@ -575,6 +577,7 @@ def run_ours(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 x fp8_e4m3 -> fp32 acc -> bf16",
         "data": "synthetic", "config": workload_config(world),
+        "tile_scheduling": "static" if args.static_tiles else "dynamic",
         "transport": {"comm": mlp.comm, "multicast": getattr(mlp, "multicast", None), "chunks": mlp.chunks,
                       "partial_dtype": str(mlp.partial_dtype).replace("torch.", "")},
         "parity": parity,
@@ -645,6 +648,8 @@ def main():
                     help="reduce and broadcast in the NVSwitch (multimem) instead of peer loads/stores; auto = from 4 ranks on")
     ap.add_argument("--cpu-tokens", type=int, default=64, help="tokens in the CPU-baseline sample")
     ap.add_argument("--cpu-tokens-single", type=int, default=4, help="tokens in the single-thread CPU sample")
+    ap.add_argument("--static-tiles", action="store_true",
+                    help="CTA-pair FP8 kernels with fixed round-robin tile shares instead of the global tile counter")
     ap.add_argument("--no-cases", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

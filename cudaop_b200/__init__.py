@@ -56,6 +56,7 @@ _SIGNATURES = {
     "b200q_nvfp4_set_tile_n": [_I],
     "b200q_nvfp4_set_2cta": [_I],
     "b200q_fp8_set_tma_store": [_I],
+    "b200q_fp8_set_dynamic_tiles": [_I],
     "b200q_fp8_set_group": [_I],
     "b200q_nvfp4_set_group": [_I],
     "b200q_sp24_set_2cta": [_I],

@@ -3,6 +3,8 @@
 #include "gemm_fp8_2cta.cuh"
 #include "../../include/b200q.h"
 
+#include <mutex>
+
 namespace b200q {
 namespace fp8 {
 
@@ -18,8 +20,40 @@ int usable_sms()
     const int n = num_sms();
     return (g_sm_limit > 0 && g_sm_limit < n) ? g_sm_limit : n;
 }
+int g_dynamic_tiles = 1;  // CTA-pair kernels take their tiles from a global counter (b200q_fp8_set_dynamic_tiles)
 int g_tma_store = 1;     // CTA-pair kernels: bf16 results through shared memory + TMA stores (0: per-thread 16-byte stores)
 int g_use_2cta = 1;      // 1 = CTA-pair kernel (tcgen05 cta_group::2) for the plain / row-col / SwiGLU GEMMs
+
+// Scheduler slots of the CTA-pair kernels: {next tile, pairs done}, zero when idle (the last pair of a launch zeroes
+// its slot again).  Launches on one stream follow each other and share a slot; launches on different streams may
+// overlap on the GPU and get different slots.  More than kSchedSlots streams: static scheduling for the rest.
+// (A CUDA graph keeps the slot of the stream it was captured on; two graphs captured on the same stream should not
+// be replayed at the same time.)
+constexpr int kSchedSlots = 64;
+__device__ uint32_t g_sched_slots[kSchedSlots][2];
+std::mutex g_sched_mu;
+struct SchedKey { int dev; cudaStream_t stream; };
+SchedKey g_sched_keys[kSchedSlots];
+int g_sched_used = 0;
+uint32_t* g_sched_base[64] = {};
+
+uint32_t* sched_slot(cudaStream_t stream)
+{
+    if (!g_dynamic_tiles) return nullptr;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_sched_mu);
+    if (g_sched_base[dev] == nullptr) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_sched_slots) != cudaSuccess) return nullptr;
+        g_sched_base[dev] = static_cast<uint32_t*>(ptr);
+    }
+    for (int i = 0; i < g_sched_used; ++i)
+        if (g_sched_keys[i].dev == dev && g_sched_keys[i].stream == stream) return g_sched_base[dev] + 2 * i;
+    if (g_sched_used == kSchedSlots) return nullptr;
+    g_sched_keys[g_sched_used] = SchedKey{dev, stream};
+    return g_sched_base[dev] + 2 * g_sched_used++;
+}
 
 template <int EPI, typename OutT, int BN, bool AR>
 cudaError_t launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmB2, const Params& p,
@@ -173,6 +207,7 @@ cudaError_t gemm(const void* A, const void* B, void* C, int M, int N, int K, int
         // bf16 results: the output as a tensor map with the epilogue's 32-row x (32- or 16-column) boxes
         CUtensorMap tC = tA;
         p.tma_store = 0;
+        p.sched = sched_slot(stream);
         if (!out_f32 && g_tma_store && (ldc * 2) % 16 == 0 && aligned16(C)) {
             const uint32_t cw = (oc % 32 == 0) ? 32u : 16u;
             const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
@@ -350,6 +385,12 @@ int b200q_fp8_set_group(int g)
 {
     if (g < 0 || g > 64) return cudaErrorInvalidValue;
     b200q::fp8::g_pair_group = g;
+    return 0;
+}
+
+int b200q_fp8_set_dynamic_tiles(int on)
+{
+    b200q::fp8::g_dynamic_tiles = on ? 1 : 0;
     return 0;
 }
 

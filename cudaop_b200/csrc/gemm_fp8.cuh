@@ -71,6 +71,7 @@ struct Params {
     int group;                   // tile rows that walk the N tiles together
     uint32_t* status;
     int tma_store;               // CTA-pair kernels: bf16 results leave through TMA stores (tensor map valid)
+    uint32_t* sched;             // CTA-pair kernels: {next tile, pairs done} for dynamic tile scheduling, or nullptr (static)
     // fused all-reduce (AR kernels only)
     const void* const* partial_ptrs;     // device array [world]: every rank's partial buffer (C is this rank's)
     __nv_bfloat16* const* out_ptrs;      // device array [world]: every rank's bf16 output

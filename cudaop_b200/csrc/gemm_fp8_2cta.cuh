@@ -17,6 +17,13 @@
 // per request instead of 16 bytes per thread; the tensor map clips at the matrix edge).
 // With the SwiGLU epilogue the leader's B half is the gate rows and the peer's the up rows, so every
 // CTA again holds gate | up of its 128 token rows side by side.
+// Tile scheduling: the leader's producer thread decides which tile the pair does next and publishes the number
+// in a 16-entry ring in both CTAs' shared memory (a DSMEM store for the peer) behind one mbarrier per entry;
+// every other role of both CTAs reads the ring.  With a scheduler slot (Params::sched) the number comes from a
+// global atomic counter, fetched one tile ahead so its latency is hidden: a pair that is slowed down — by another
+// kernel sharing its SMs, such as the all-reduce of the previous step — simply takes fewer tiles instead of
+// holding the whole grid up with a fixed share.  The last pair to finish resets the slot for the next launch.
+// Without a slot the sequence is the static pair, pair + pairs, ...
 #pragma once
 #include <type_traits>
 
@@ -34,7 +41,7 @@ struct PairCfg {
     static constexpr int kStageBytes = kBM * kBK + kBHalfRows * kBK;    // A 16 KiB + B half (16 or 14 KiB)
     static constexpr int kStages = 6;
     static constexpr int kStoreBytes = 4 * 2 * 2048;                    // per epilogue warp two 32-row x 64-byte staging buffers
-    static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStoreBytes + 1024 + 512;    // + alignment slack + barriers and tile ring
     static_assert(kStageBytes % 1024 == 0 && BN % 32 == 0, "tile shape");
 };
 
@@ -59,6 +66,10 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     const uint32_t tmem_slot = bar_base + 8u * (2 * kStages + 4);
     volatile uint32_t* tmem_slot_ptr =
         reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - ptx::smem_u32(smem_raw)));
+    constexpr int kRing = 16;
+    auto sched_bar = [&](int i) { return bar_base + 8u * (2 * kStages + 5 + i); };     // tile-ring entry i has been written
+    const uint32_t ring = bar_base + 8u * (2 * kStages + 5 + kRing);                    // kRing tile numbers
+    volatile int* ring_ptr = reinterpret_cast<volatile int*>(smem_raw + (ring - ptx::smem_u32(smem_raw)));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta_rank = ptx::cluster_ctarank();          // 0 = leader of the pair
@@ -71,8 +82,18 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
         for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull_bar(b), 1); ptx::mbar_init(tempty_bar(b), 8); }
+        for (int i = 0; i < kRing; ++i) ptx::mbar_init(sched_bar(i), 1);
         ptx::fence_mbar_init();
     }
+    // The t-th tile of this pair, as published by the leader's producer (>= num_tiles: no more).  An entry is
+    // overwritten kRing tiles later, when every reader is past it: the leader's producer is at most kStages K-blocks
+    // (with a short K: that many tiles) ahead of the peer's producer and of the MMA thread, which is at most two
+    // accumulators ahead of the epilogue — nine tiles at the very most.
+    static_assert(kRing >= kStages + 4, "tile ring depth");
+    auto tile_at = [&](int t, uint32_t site, bool& ok) -> int {
+        if (!ptx::mbar_wait(sched_bar(t & (kRing - 1)), (t / kRing) & 1u, p.status, site)) { ok = false; return num_tiles; }
+        return ring_ptr[t & (kRing - 1)];
+    };
     if (warp == 1) { ptx::tmem_alloc_2cta(tmem_slot, kTmemCols); ptx::tmem_relinquish_2cta(); }
     ptx::tcgen05_fence_before_sync();
     ptx::cluster_arrive();          // both CTAs' barriers are initialised before anyone signals across the pair
@@ -87,7 +108,26 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             ptx::tma_prefetch_desc(&tmB);
             if (EPI == kEpiSwiGLU) ptx::tma_prefetch_desc(&tmB2);
             int stage = 0; uint32_t phase = 0; bool ok = true;
-            for (int tile = pair; tile < num_tiles && ok; tile += pairs) {
+            int static_next = pair;
+            auto fetch = [&]() -> int {                     // leader only: the next tile of this pair
+                if (p.sched != nullptr) return static_cast<int>(atomicAdd(p.sched, 1u));
+                const int t = static_next; static_next += pairs; return t;
+            };
+            int ahead = (cta_rank == 0) ? fetch() : 0;
+            for (int t = 0; ok; ++t) {
+                int tile;
+                if (cta_rank == 0) {
+                    tile = ahead < num_tiles ? ahead : num_tiles;
+                    const int e = t & (kRing - 1);
+                    ring_ptr[e] = tile;
+                    ptx::st_shared_cluster_u32(ptx::mapa(ring + 4u * e, 1), static_cast<uint32_t>(tile));
+                    ptx::mbar_arrive(sched_bar(e));
+                    ptx::mbar_arrive_cluster(ptx::mapa(sched_bar(e), 1));           // release: the peer sees the entry
+                    if (tile < num_tiles) ahead = fetch();                          // for the next round; not waited for here
+                } else {
+                    tile = tile_at(t, 9, ok);
+                }
+                if (tile >= num_tiles) break;
                 int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
                 const int m0 = tm * kPairBM + static_cast<int>(cta_rank) * kBM;
                 const int n0 = tn * kOutCols;
@@ -105,6 +145,13 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                     if (++stage == kStages) { stage = 0; phase ^= 1u; }
                 }
             }
+            // dynamic scheduling: every pair fetched exactly one number >= num_tiles (or gave up); the last pair to get
+            // here leaves the slot zeroed for the next launch on this stream
+            if (cta_rank == 0 && p.sched != nullptr) {
+                if (!ok) { while (ahead < num_tiles) ahead = fetch(); }          // drain, so that every pair's last fetch is a terminating one
+                __threadfence();
+                if (atomicAdd(p.sched + 1, 1u) + 1u == static_cast<uint32_t>(pairs)) { p.sched[0] = 0u; p.sched[1] = 0u; __threadfence(); }
+            }
             if (!ok) __nanosleep(200000);
         }
     } else if (warp == 1) {
@@ -112,8 +159,8 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         if (cta_rank == 0 && ptx::elect_one()) {
             constexpr uint32_t idesc = (EPI == kEpiInt32) ? ptx::umma_idesc_i8(kPairBM, kPairBN) : ptx::umma_idesc(0, 0, kPairBM, kPairBN);
             int stage = 0; uint32_t phase = 0; bool ok = true;
-            int t = 0;
-            for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
+            for (int t = 0; ok; ++t) {
+                if (tile_at(t, 10, ok) >= num_tiles) break;
                 const int buf = t & 1;
                 if (!ptx::mbar_wait(tempty_bar(buf), ((t >> 1) & 1u) ^ 1u, p.status, 2)) { ok = false; break; }
                 ptx::tcgen05_fence_after_sync();
@@ -148,8 +195,10 @@ gemm_fp8_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const uint32_t stage_buf = store_base + static_cast<uint32_t>(q) * 4096u;
         const uint64_t store_policy = ptx::l2_policy_evict_first();
         uint32_t chunk_no = 0;
-        int t = 0; bool ok = true;
-        for (int tile = pair; tile < num_tiles && ok; tile += pairs, ++t) {
+        bool ok = true;
+        for (int t = 0; ok; ++t) {
+            const int tile = tile_at(t, 11, ok);
+            if (tile >= num_tiles) break;
             const int buf = t & 1;
             int tm, tn; tile_coords(tile, p.tiles_m, p.tiles_n, p.group, tm, tn);
             const int row = tm * kPairBM + static_cast<int>(cta_rank) * kBM + q * 32 + lane;

@@ -464,6 +464,11 @@ __device__ __forceinline__ uint32_t mapa(uint32_t smem_addr, uint32_t cta_rank)
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta_rank));
     return r;
 }
+// st.shared::cluster.u32: a store into the shared memory of any CTA of the cluster (address from mapa)
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v)
+{
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void cluster_arrive()
 {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");

@@ -20,14 +20,18 @@
 namespace cudaop_b200 {
 namespace {
 
+// Numbers go into error messages as ready-made strings: formatting them through an output stream (which is what the
+// TORCH_CHECK macros do with non-string arguments) crashed inside the C++ runtime's locale code in this process.
+std::string num(int64_t v) { return std::to_string(v); }
+
 void check_cuda_2d(const torch::Tensor& t, const char* name, std::initializer_list<c10::ScalarType> dtypes, int64_t dim = 2)
 {
+    TORCH_CHECK_VALUE(t.dim() == dim, name, " must have ", num(dim), " dimensions, got ", num(t.dim()));
     TORCH_CHECK_VALUE(t.is_cuda(), name, " must be a CUDA tensor");
-    TORCH_CHECK_VALUE(t.dim() == dim, name, " must have ", dim, " dimensions, got ", t.dim());
     TORCH_CHECK_VALUE(t.is_contiguous(), name, " must be contiguous");
     bool ok = false;
     for (auto d : dtypes) ok = ok || t.scalar_type() == d;
-    TORCH_CHECK_VALUE(ok, name, " has dtype ", t.scalar_type(), ", which this operator does not take");
+    TORCH_CHECK_VALUE(ok, name, " has dtype ", c10::toString(t.scalar_type()), ", which this operator does not take");
 }
 
 void same_device(std::initializer_list<const torch::Tensor*> ts)
@@ -43,7 +47,7 @@ void* stream_of(const torch::Tensor& t)
 
 void raise_on(int code, const char* what)
 {
-    TORCH_CHECK(code == 0, what, " failed with cudaError ", code, code == 1 ? " (invalid argument)" : "");
+    TORCH_CHECK(code == 0, what, " failed with cudaError ", num(code), code == 1 ? " (invalid argument)" : "");
     C10_CUDA_KERNEL_LAUNCH_CHECK();
 }
 
@@ -65,7 +69,7 @@ torch::Tensor out_like(const torch::Tensor& ref, std::vector<int64_t> shape, c10
 torch::Tensor gemm_fp8(torch::Tensor a, torch::Tensor b, double scale_a, double scale_b)
 {
     check_cuda_2d(a, "a", {kU8, kE4M3}); check_cuda_2d(b, "b", {kU8, kE4M3}); same_device({&a, &b});
-    TORCH_CHECK_VALUE(a.size(1) == b.size(1), "inner dimensions differ: ", a.size(1), " vs ", b.size(1));
+    TORCH_CHECK_VALUE(a.size(1) == b.size(1), "inner dimensions differ: ", num(a.size(1)), " vs ", num(b.size(1)));
     const c10::cuda::CUDAGuard guard(a.device());
     auto c = out_like(a, {a.size(0), b.size(0)}, kBF16);
     raise_on(b200q_gemm_fp8(a.data_ptr(), b.data_ptr(), c.data_ptr(), (int)a.size(0), (int)b.size(0), (int)a.size(1),
@@ -76,7 +80,7 @@ torch::Tensor gemm_fp8(torch::Tensor a, torch::Tensor b, double scale_a, double 
 torch::Tensor gemm_i8(torch::Tensor a, torch::Tensor b, c10::optional<torch::Tensor> c)
 {
     check_cuda_2d(a, "a", {kI8}); check_cuda_2d(b, "b", {kI8}); same_device({&a, &b});
-    TORCH_CHECK_VALUE(a.size(1) == b.size(1), "inner dimensions differ: ", a.size(1), " vs ", b.size(1));
+    TORCH_CHECK_VALUE(a.size(1) == b.size(1), "inner dimensions differ: ", num(a.size(1)), " vs ", num(b.size(1)));
     const void* cin = nullptr;
     if (c.has_value()) {
         check_cuda_2d(*c, "c", {kI32}); same_device({&a, &*c});

@@ -146,6 +146,8 @@ int b200q_allreduce_set_reserved_smem(int bytes);
 int b200q_fp8_set_2cta(int on);        /* FP8 GEMMs on CTA pairs (tcgen05 cta_group::2, 256-row tiles); default on */
 int b200q_fp8_set_group(int g);        /* CTA-pair FP8 kernels: tile rows (of 256) that share a pass over the N tiles; 0 = auto */
 int b200q_nvfp4_set_group(int g);      /* the same for the CTA-pair NVFP4 kernel */
+int b200q_fp8_set_dynamic_tiles(int on);   /* CTA-pair FP8 kernels: tiles handed out by a global counter, so a pair slowed down by a
+                                            * co-running kernel takes fewer tiles (default on); off: fixed round-robin shares */
 int b200q_fp8_set_tma_store(int on);   /* CTA-pair FP8 kernels: bf16 results via shared memory + TMA stores (default on) */
 int b200q_fp8_set_reducer_stride(int stride);   /* fused all-reduce: every stride-th CTA reduces, 1..16 */
 int b200q_nvfp4_set_tile_n(int bn);

@@ -64,3 +64,15 @@ def test_missing_extension_is_a_loud_error(monkeypatch):
         assert False, "expected ImportError"
     except ImportError:
         pass
+
+
+def test_extension_error_messages_with_numbers_are_exceptions_not_crashes():
+    """Numbers in the extension's error messages are formatted with std::to_string: streaming them (the TORCH_CHECK
+    default) crashed the process.  Checked here without a GPU through the dimension check, which comes first."""
+    import pytest
+    import torch
+    import cudaop_b200 as ops
+    with pytest.raises(ValueError, match="2 dimensions, got 1"):
+        ops.gemm_fp8(torch.zeros(16, dtype=torch.uint8), torch.zeros((4, 16), dtype=torch.uint8), 1.0, 1.0)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        ops.gemm_fp8(torch.zeros((4, 16), dtype=torch.uint8), torch.zeros((4, 16), dtype=torch.uint8), 1.0, 1.0)

@@ -64,6 +64,21 @@ def test_argument_checks_raise_value_errors():
     torch.cuda.synchronize()
 
 
+def test_a_refusal_by_the_c_abi_is_a_runtime_error():
+    """An argument the tensor checks let through but the library refuses (here: a scale group size it does not
+    implement) comes back as cudaErrorInvalidValue and must surface as an exception carrying that code."""
+    import cudaop_b200 as ops
+    x = torch.zeros((1, 256), dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros((32, 128), dtype=torch.uint8, device="cuda")
+    s = torch.zeros((32, 4), dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="cudaError 1"):
+        ops.gemm_w4a16(x, w, s, 64)
+    with pytest.raises(ValueError, match="inner dimensions differ: 128 vs 64"):
+        a = torch.zeros((128, 128), dtype=torch.uint8, device="cuda")
+        ops.gemm_fp8(a, a[:, :64].contiguous(), 1.0, 1.0)
+    torch.cuda.synchronize()
+
+
 def test_launches_on_the_current_stream():
     """The result of a call made on a side stream is complete once that stream is synchronised, with work queued
     in front of it on that stream only."""
