@@ -382,7 +382,15 @@ def gemm_cases(peaks):
             out["w4a16_m1_pdl"] = {"us": ms * 1e3, "gbs": gbs, "frac_measured_hbm": gbs / peaks["hbm_gbs"],
                                    "frac_nominal_7700": gbs / NOMINAL["hbm_gbs"], "bytes": byts,
                                    "note": "as w4a16_m1, calls chained with programmatic dependent launch (b200q_w4a16_set_pdl)"}
-    del wq, sc
+    # W4A16 at a prefill shape: 4096 tokens (tcgen05 kernel, integer weights, group scales on the fp32 partial sums)
+    Mp = 4096
+    xp = torch.randn((Mp, K), device="cuda").to(torch.bfloat16)
+    yp = torch.empty((Mp, N), dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize(); time.sleep(1.0)
+    ms = time_loop(lambda: L.b200q_gemm_w4a16(xp.data_ptr(), wq[0].data_ptr(), sc[0].data_ptr(), yp.data_ptr(), Mp, N, K, 128, st()), 20)
+    tf = 2 * Mp * N * K / ms / 1e9
+    out["w4a16_prefill_4096"] = {"ms": ms, "tflops": tf, "frac_nominal_bf16_2250": tf / 2250.0, "frac_measured_bf16": tf / peaks["bf16_tflops"]}
+    del wq, sc, xp, yp
     torch.cuda.empty_cache()
     return out
 
@@ -423,7 +431,8 @@ def multi_rank_parity(mlp, x, rank, world, dev):
     dist_ulp = ((yf - wf).abs() / ulp)[big].max()
     out = {"replicas_equal": bool(eq.item()), "exact_frac": float((y == want).float().mean().item()),
            "max_ulp_vs_rank_order_sum": float(dist_ulp.item()),
-           "transport": "multimem (in-switch reduction)" if getattr(mlp, "multicast", False) else "peer loads/stores",
+           "transport": ("multimem (in-switch reduction)" if getattr(mlp, "multicast", False) else "peer loads/stores") +
+                        (", result gathered by copy engines" if mlp.comm == "pipelined_ce" else ""),
            "comm": mlp.comm}
     if rank == 0:
         g = torch.Generator().manual_seed(11)
@@ -592,7 +601,7 @@ def run_ours(args):
         "latency_ms_per_forward": ms_latency,
         "overlap": ("steps are independent batches: the all-reduce of step i runs on a side stream under the GEMMs "
                     "of step i+1 (double-buffered); latency_ms_per_forward is one forward alone with the all-reduce "
-                    "fused into the down-projection kernel") if world > 1 and mlp.comm == "pipelined" else "none",
+                    "fused into the down-projection kernel") if world > 1 and mlp.comm.startswith("pipelined") else "none",
         "gpu_launches": launches, "kernels_ms": kernels_ms,
         "roofline": {"bound": "tensor", "kernel": "gemm_fp8_2cta_kernel<SwiGLU> (gate/up projection, CTA pairs)",
                      "achieved": top_tf, "peak": peak_burst, "unit": "TFLOP/s", "frac": top_tf / peak_burst,
@@ -640,7 +649,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chunks", type=int, default=4, help="token chunks for all-reduce overlap (N > 1)")
-    ap.add_argument("--comm", default="pipelined", choices=["auto", "pipelined", "fused", "symm", "nccl"],
+    ap.add_argument("--comm", default="pipelined", choices=["auto", "pipelined", "pipelined_ce", "fused", "symm", "nccl"],
                     help="all-reduce: the library's NVSwitch kernel over symmetric memory, or NCCL")
     ap.add_argument("--ar-ctas", type=int, default=None, help="CTAs of the stand-alone all-reduce kernel (default: by transport)")
     ap.add_argument("--partial", default="bf16", choices=["bf16", "fp32"], help="dtype of the partial outputs that cross NVLink")

@@ -1,6 +1,6 @@
-// gemm_w4a16_bf16 — INT4 weight-only decode GEMM (group-128 fp16 scales, bf16 activations/out):
+// gemm_w4a16_bf16 — INT4 weight-only GEMM (group-128 fp16 scales, bf16 activations/out):
 // full correctness against the host reference, single-call latency, and streaming bandwidth over
-// a stack of distinct weight sets larger than L2.
+// a stack of distinct weight sets larger than L2 (decode shapes) or TFLOP/s (the prefill shape).
 #include "bench_common.h"
 using namespace bench;
 
@@ -26,7 +26,7 @@ static bool run_case(const Case& c, const Args& a)
         }
     std::vector<float> Xf = normal((size_t)M * K, a.seed + 7);
     for (size_t i = 0; i < X.size(); ++i) { X[i] = f32_to_bf16(Xf[i]); Xf[i] = bf16_to_f32(X[i]); }
-    const int sets = a.profile ? 2 : 72;                       // 72 x 8 MiB of weights > L2
+    const int sets = a.profile ? 2 : (M > 16 ? 8 : 72);        // 72 x 8 MiB of weights > L2
     uint8_t* dW; uint16_t* dS; CK(cudaMalloc(&dW, (size_t)sets * Wq.size())); CK(cudaMalloc(&dS, (size_t)sets * S.size() * 2));
     for (int s = 0; s < sets; ++s) {
         CK(cudaMemcpy(dW + (size_t)s * Wq.size(), Wq.data(), Wq.size(), cudaMemcpyHostToDevice));
@@ -54,7 +54,8 @@ static bool run_case(const Case& c, const Args& a)
         std::printf("[BENCHMARK] isolated call latency ms: mean %.4f median %.4f min %.4f\n", t.mean_ms, t.median_ms, t.min_ms);
         std::printf("[BENCHMARK] streaming %d weight sets back to back: %.3f us per call, %.1f GB/s = %.1f %% of measured HBM copy (6453) = %.1f %% of nominal (7700)\n",
                     sets, ms * 1e3, bytes / ms / 1e6, 100 * bytes / ms / 1e6 / 6453, 100 * bytes / ms / 1e6 / 7700);
-        std::printf("{\"op\":\"gemm_w4a16_bf16\",\"case\":\"%s\",\"M\":%d,\"N\":%d,\"K\":%d,\"us_per_call\":%.4f,\"gbs\":%.1f}\n", c.name, M, N, K, ms * 1e3, bytes / ms / 1e6);
+        if (M > 16) std::printf("[BENCHMARK] %.1f TFLOP/s (2 M N K per call)\n", 2.0 * M * N * K / ms / 1e9);
+        std::printf("{\"op\":\"gemm_w4a16_bf16\",\"case\":\"%s\",\"M\":%d,\"N\":%d,\"K\":%d,\"us_per_call\":%.4f,\"gbs\":%.1f,\"tflops\":%.2f}\n", c.name, M, N, K, ms * 1e3, bytes / ms / 1e6, 2.0 * M * N * K / ms / 1e9);
     }
     cudaFree(dW); cudaFree(dS); cudaFree(dX); cudaFree(dY); cudaStreamDestroy(st);
     return ok;
@@ -63,7 +64,7 @@ static bool run_case(const Case& c, const Args& a)
 int main(int argc, char** argv)
 {
     Args a = parse(argc, argv);
-    std::vector<Case> cases = {{"decode_m1", 1, 4096, 4096}, {"decode_m16", 16, 4096, 4096}};
+    std::vector<Case> cases = {{"decode_m1", 1, 4096, 4096}, {"decode_m16", 16, 4096, 4096}, {"prefill_m512", 512, 4096, 4096}};
     if (a.m > 0 && a.n > 0 && a.k > 0) cases = {{"custom", a.m, a.n, a.k}};
     bool ok = true;
     for (const Case& c : cases)

@@ -58,8 +58,11 @@ __device__ __forceinline__ bool rank_barrier(const Params& p, int phase, int cta
     return __syncthreads_and(ok);
 }
 
-// The work of CTA `cta` of `nctas` on rank p.rank.
-template <bool MC, bool PartialBf16, int UNROLL>
+// The work of CTA `cta` of `nctas` on rank p.rank.  SCATTER: the reduce-scatter half alone — the rank's slice of
+// the sum goes to its OWN output buffer only and there is no end barrier; the ranks then complete each other's
+// outputs with copy-engine copies ordered behind a b200q_rank_barrier, which take no SM time from a GEMM running
+// beside them.
+template <bool MC, bool PartialBf16, int UNROLL, bool SCATTER = false>
 __device__ __forceinline__ void allreduce_body(const Params& p, int cta, int nctas)
 {
     const int nthreads = blockDim.x;          // 128..512: small blocks on every SM disturb a co-running GEMM evenly
@@ -78,10 +81,13 @@ __device__ __forceinline__ void allreduce_body(const Params& p, int cta, int nct
         arc::reduce8xU<MC, PartialBf16, UNROLL>(reinterpret_cast<const void* const*>(p.partial_ptrs), p.partial_mc, p.world,
                                                 e, valid, o);
 #pragma unroll
-        for (int u = 0; u < UNROLL; ++u)
-            if (valid[u]) arc::broadcast8<MC>(p.out_ptrs, p.out_mc, p.world, e[u], o[u]);
+        for (int u = 0; u < UNROLL; ++u) {
+            if (!valid[u]) continue;
+            if (SCATTER) *reinterpret_cast<uint4*>(p.out_ptrs[p.rank] + e[u]) = o[u];
+            else arc::broadcast8<MC>(p.out_ptrs, p.out_mc, p.world, e[u], o[u]);
+        }
     }
-    rank_barrier(p, 1, cta);
+    if (!SCATTER) rank_barrier(p, 1, cta);
 }
 
 template <bool MC, bool PartialBf16, int UNROLL>
@@ -89,6 +95,13 @@ __global__ void __launch_bounds__(kThreads)
 allreduce_to_bf16_kernel(const Params p)
 {
     allreduce_body<MC, PartialBf16, UNROLL>(p, blockIdx.x, gridDim.x);
+}
+
+template <bool MC, bool PartialBf16>
+__global__ void __launch_bounds__(kThreads)
+reduce_scatter_to_bf16_kernel(const Params p)
+{
+    allreduce_body<MC, PartialBf16, 4, true>(p, blockIdx.x, gridDim.x);
 }
 
 // Every rank of a small world inside ONE launch on ONE device: CTAs [r * ctas, (r + 1) * ctas) play rank r on
@@ -158,6 +171,37 @@ int b200q_allreduce_to_bf16(const void* const* partial_ptrs_dev, void* const* ou
     else { if (mc) B200Q_AR_U(true, false); else B200Q_AR_U(false, false); }
 #undef B200Q_AR_U
 #undef B200Q_AR
+    return cudaGetLastError();
+}
+
+int b200q_reduce_scatter_to_bf16(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                 void* const* signal_ptrs_dev, const void* partial_multicast, int partial_is_bf16,
+                                 long long elem_offset, long long elems, int rank, int world, unsigned int epoch,
+                                 unsigned int signal_offset_bytes, int ctas, void* stream)
+{
+    using namespace b200q;
+    if (partial_ptrs_dev == nullptr || out_ptrs_dev == nullptr || signal_ptrs_dev == nullptr) return cudaErrorInvalidValue;
+    if (world < 1 || world > ar::kMaxWorld || rank < 0 || rank >= world) return cudaErrorInvalidValue;
+    if (elems <= 0 || elem_offset < 0 || elems % (8LL * world) != 0 || elem_offset % 8 != 0) return cudaErrorInvalidValue;
+    if (ctas < 1 || ctas > ar::kMaxCtas || signal_offset_bytes % 4 != 0) return cudaErrorInvalidValue;
+    ar::Params p{};
+    p.partial_ptrs = reinterpret_cast<const float* const*>(partial_ptrs_dev);
+    p.out_ptrs = reinterpret_cast<__nv_bfloat16* const*>(out_ptrs_dev);
+    p.signal_ptrs = reinterpret_cast<uint32_t* const*>(signal_ptrs_dev);
+    p.partial_mc = static_cast<const float*>(partial_multicast);
+    p.offset = elem_offset; p.elems = elems; p.epoch = epoch; p.pad_offset_words = signal_offset_bytes / 4;
+    p.rank = rank; p.world = world;
+    p.status = status_ptr();
+    if (p.status == nullptr) return cudaErrorInvalidDevice;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool mc = partial_multicast != nullptr;
+    if (partial_is_bf16) {
+        if (mc) ar::reduce_scatter_to_bf16_kernel<true, true><<<ctas, ar::g_threads, 0, s>>>(p);
+        else ar::reduce_scatter_to_bf16_kernel<false, true><<<ctas, ar::g_threads, 0, s>>>(p);
+    } else {
+        if (mc) ar::reduce_scatter_to_bf16_kernel<true, false><<<ctas, ar::g_threads, 0, s>>>(p);
+        else ar::reduce_scatter_to_bf16_kernel<false, false><<<ctas, ar::g_threads, 0, s>>>(p);
+    }
     return cudaGetLastError();
 }
 

@@ -103,18 +103,18 @@ class TensorParallelMLP:
         self._epoch = 0
         if world > 1:
             self.comm = comm
-            if comm in ("auto", "fused", "symm", "pipelined"):
+            if comm in ("auto", "fused", "symm", "pipelined", "pipelined_ce"):
                 try:
-                    self._nbuf = 2 if comm == "pipelined" else 1
+                    self._nbuf = 2 if comm.startswith("pipelined") else 1
                     self._init_symmetric(T, H)
-                    self.comm = comm if comm in ("symm", "pipelined") else "fused"
+                    self.comm = comm if comm in ("symm", "pipelined", "pipelined_ce") else "fused"
                 except Exception as exc:
                     if comm != "auto":
                         raise
                     warnings.warn(f"symmetric memory is not available ({type(exc).__name__}: {exc}); "
                                   "the all-reduce falls back to NCCL on fp32 partials")
                     self.comm = "nccl"
-            if self.comm in ("fused", "pipelined"):
+            if self.comm in ("fused", "pipelined", "pipelined_ce"):
                 self.chunks = 1
             self._buf = 0
             self._ar_done = [None, None]
@@ -141,7 +141,8 @@ class TensorParallelMLP:
         self.partial = self._partial_all[0]
         self.y_sym = self._y_all[0]
         self._fused_flag_offset = ops.lib().b200q_allreduce_signal_bytes()
-        nflags = (self._fused_flag_offset + ops.lib().b200q_fused_allreduce_flag_bytes()) // 4
+        self._bar_offset = self._fused_flag_offset + ops.lib().b200q_fused_allreduce_flag_bytes()
+        nflags = (self._bar_offset + ops.lib().b200q_rank_barrier_signal_bytes()) // 4
         self._counters = torch.zeros((ops.lib().b200q_fused_allreduce_counter_bytes() // 4,), dtype=torch.int32, device=dev)
         self.flags = symm.empty((nflags,), dtype=torch.int32, device=dev)
         self.flags.zero_()
@@ -149,6 +150,11 @@ class TensorParallelMLP:
         self._hy = symm.rendezvous(self._y_all, group)
         self._hf = symm.rendezvous(self.flags, group)
         self.multicast = self.use_multicast and bool(self._hp.multicast_ptr) and bool(self._hy.multicast_ptr)
+        # every peer's output buffers as tensors this rank can copy from (copy-engine half of "pipelined_ce")
+        self._y_peer = [self._hy.get_buffer(r, (nb, T, H), torch.bfloat16, 0) if r != self.rank else None
+                        for r in range(self.world)]
+        self._ce_streams = [torch.cuda.Stream(device=dev) for _ in range(min(4, self.world - 1))]
+        self._bar_epoch = 0
         # launch shape of the stand-alone all-reduce kernel, from measurements at 2/4/8 ranks: the
         # in-switch reduction saturates with few threads (and then disturbs a co-running GEMM least),
         # peer loads need many requests in flight from every SM
@@ -231,7 +237,7 @@ class TensorParallelMLP:
         T, H = x.shape
         if H != self.hidden or T > self.max_tokens:
             raise ValueError(f"x must be [<= {self.max_tokens}, {self.hidden}]")
-        if self.comm == "pipelined":
+        if self.comm in ("pipelined", "pipelined_ce"):
             return self._forward_pipelined(x, T)
         if self.comm in ("symm", "fused"):
             y = self.y_sym[:T]
@@ -285,12 +291,49 @@ class TensorParallelMLP:
             done = torch.cuda.Event(); done.record(main)
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(done)
-                self._allreduce_chunk(0, T, buf=b)
+                if self.comm == "pipelined_ce":
+                    launches += self._reduce_scatter_then_copies(T, b)
+                else:
+                    self._allreduce_chunk(0, T, buf=b)
                 ev = torch.cuda.Event(); ev.record(self.comm_stream)
             self._ar_done[b] = ev
             self.output_ready = ev
         self.kernel_launches_per_forward = launches + 1
         return self._y_all[b][:T]
+
+    def _reduce_scatter_then_copies(self, T, b):
+        """The exchange in two phases on the side stream: a kernel sums this rank's 1/R of the output into its own
+        buffer, a barrier over the ranks follows, and the other ranks' parts arrive by device-to-device copies
+        (copy engines, no SM time).  A rank overwrites its part of buffer b two steps later, behind the start
+        barrier of that step's kernel, which every peer passes only after its own copies of this step.
+        Returns the number of extra kernel launches (the barrier)."""
+        L = ops.lib(); H = self.hidden
+        n = T * H
+        if n % (8 * self.world) != 0:
+            raise ValueError("tokens * hidden must be divisible by 8 * world")
+        cs = self.comm_stream
+        self._epoch += 1
+        mc_p = self._hp.multicast_ptr if self.multicast else None
+        ops._raise(L.b200q_reduce_scatter_to_bf16(
+            self._hp.buffer_ptrs_dev, self._hy.buffer_ptrs_dev, self._hf.buffer_ptrs_dev, mc_p,
+            int(self.partial_dtype == torch.bfloat16), b * self.max_tokens * H, n, self.rank, self.world, self._epoch, 0,
+            self.ar_ctas, cs.cuda_stream), "b200q_reduce_scatter_to_bf16")
+        self._bar_epoch += 1
+        ops._raise(L.b200q_rank_barrier(self._hf.buffer_ptrs_dev, self.rank, self.world, self._bar_epoch, self._bar_offset,
+                                        cs.cuda_stream), "b200q_rank_barrier")
+        reduced = torch.cuda.Event(); reduced.record(cs)
+        per = n // self.world
+        mine = self._y_all[b].view(-1)
+        k = 0
+        for d in range(1, self.world):                     # start with the next rank, so the pulls spread over the links
+            r = (self.rank + d) % self.world
+            st = self._ce_streams[k % len(self._ce_streams)]; k += 1
+            st.wait_event(reduced)
+            with torch.cuda.stream(st):
+                mine[r * per:(r + 1) * per].copy_(self._y_peer[r][b].view(-1)[r * per:(r + 1) * per], non_blocking=True)
+        for st in self._ce_streams:
+            cs.wait_stream(st)
+        return 1
 
     def wait(self):
         """Makes the current stream wait for every all-reduce issued so far (no host synchronisation)."""

@@ -154,7 +154,9 @@ int b200q_nvfp4_set_tile_n(int bn);
 int b200q_nvfp4_set_2cta(int on);      /* NVFP4 GEMM on CTA pairs (256 x 192 / 256 x 256 tiles per pair) when M > 128 and the
                                         * tile width is not 128; default on */
 int b200q_w4a16_set_impl(int impl);     /* 0 = by M (default): streaming CUDA-core GEMV for one token (the older GEMV forms when K is not
-                                         * a multiple of 2048 or exceeds 16384), warp-MMA kernel above;
+                                         * a multiple of 2048 or exceeds 16384), warp-MMA kernel for 2..16 tokens, tcgen05
+                                         * prefill kernel (group-wise partial-sum scaling) above 16; 5 / 6 = the streaming
+                                         * GEMV / the prefill kernel wherever they apply;
                                          * 1 = tcgen05 kernel; 2 = warp-MMA kernel for every M; 3 / 4 = the two GEMV forms
                                          * (shared memory + dp4a / registers + fp32) for up to 4 tokens */
 int b200q_w4a16_set_pdl(int on);        /* programmatic dependent launch of the GEMV / tcgen05 W4A16 kernels (default off):
@@ -189,6 +191,16 @@ int b200q_allreduce_to_bf16(const void* const* partial_ptrs_dev, void* const* ou
                             void* const* signal_ptrs_dev, const void* partial_multicast, void* out_multicast,
                             int partial_is_bf16, long long elem_offset, long long elems, int rank, int world,
                             unsigned int epoch, unsigned int signal_offset_bytes, int ctas, void* stream);
+/* The reduce-scatter half of the same exchange: rank r's call sums elements [elem_offset + r * elems / world,
+ * elem_offset + (r + 1) * elems / world) of every rank's partial buffer (same arithmetic and rounding) and stores
+ * them to the same range of its OWN output buffer only; nothing is broadcast and there is no end barrier.  A
+ * caller completes the other ranges with device-to-device copies from the peers' output buffers (copy engines:
+ * no SM is taken from a GEMM running beside them), ordered behind a b200q_rank_barrier on the same stream.
+ * Together they are the ncclAllReduce of op/nccl/nccl_mlp_test.cu:181-195 split into its two phases. */
+int b200q_reduce_scatter_to_bf16(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                 void* const* signal_ptrs_dev, const void* partial_multicast, int partial_is_bf16,
+                                 long long elem_offset, long long elems, int rank, int world, unsigned int epoch,
+                                 unsigned int signal_offset_bytes, int ctas, void* stream);
 int b200q_allreduce_set_unroll(int unroll);     /* tuning knob: independent reductions in flight per thread, 1..8 */
 int b200q_allreduce_set_threads(int threads);   /* tuning knob: threads per CTA of the all-reduce kernel, 128/256/512 */
 size_t b200q_allreduce_signal_bytes(void);

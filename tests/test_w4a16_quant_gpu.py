@@ -98,6 +98,54 @@ def test_one_token_streaming_form_propagates_non_finite_activations(impl):
     assert torch.isnan(out.float()).all()                  # Inf * 0-weight terms make the reference NaN as well
 
 
+@pytest.mark.parametrize("shape", [(17, 128, 128), (64, 256, 256), (200, 130, 1152), (129, 1000, 384), (512, 4096, 4096),
+                                   (300, 72, 16384), (2, 40, 256)])
+def test_prefill_form(shape, impl):
+    """The tcgen05 prefill kernel (integer weights on the tensor core, the group's scale applied to its fp32 partial
+    sum): ragged token and row counts, one to 128 groups; every output against the oracle."""
+    import cudaop_b200 as ops
+    if impl != (0, 0):
+        pytest.skip("selects its own implementation")
+    M, N, K = shape
+    ops.lib().b200q_w4a16_set_impl(6)
+    xb, wq, s = oracle.make_w4a16_case(M, N, K, seed=M + N + K)
+    out = ops.gemm_w4a16(dev(xb, torch.bfloat16), dev(wq), dev(s, torch.float16))
+    torch.cuda.synchronize()
+    assert ops.status() == 0
+    assert_bar(bf16_to_f32(out), _w4_ref(xb, wq, s), K, f"prefill {shape}")
+
+
+def test_prefill_known_answer_and_default_dispatch(impl):
+    """Coordinate-dependent S4 values (op/test/arch_primitives/ptx_mma_integer.cu:61-74) with scales 1 and 0.5 per
+    group: every product and sum is exact, so the output equals bf16(expected) bit for bit; 48 tokens go to the
+    prefill kernel by default."""
+    import cudaop_b200 as ops
+    if impl != (0, 0):
+        pytest.skip("default dispatch only")
+    M, N, K = 48, 40, 256
+    W = np.array([[((n * 5 + k * 3 + 2) % 15) - 7 for k in range(K)] for n in range(N)], np.int8)
+    X = np.array([[((m * 2 + k * 7 + 4) % 15) - 7 for k in range(K)] for m in range(M)], np.float32)
+    s = np.full((N, K // 128), 1.0, np.float32); s[:, 1] = 0.5
+    out = ops.gemm_w4a16(dev(oracle.encode_bf16(X), torch.bfloat16), dev(oracle.pack_s4(W)), dev(oracle.encode_f16(s), torch.float16))
+    torch.cuda.synchronize()
+    want = X[:, :128] @ W[:, :128].T.astype(np.float32) + 0.5 * (X[:, 128:] @ W[:, 128:].T.astype(np.float32))
+    assert np.array_equal(bf16_to_f32(out), oracle.decode_bf16(oracle.encode_bf16(want)))
+
+
+def test_prefill_full_size_sampled_rows(impl):
+    import cudaop_b200 as ops
+    if impl != (0, 0):
+        pytest.skip("default dispatch only")
+    M, N, K = 4096, 4096, 4096
+    xb, wq, s = oracle.make_w4a16_case(M, N, K, seed=77)
+    out = ops.gemm_w4a16(dev(xb, torch.bfloat16), dev(wq), dev(s, torch.float16))
+    torch.cuda.synchronize()
+    assert ops.status() == 0
+    rows = np.random.default_rng(1).choice(M, 256, replace=False)
+    ref = oracle.gemm_f32(oracle.decode_bf16(xb[rows]), oracle.dequant_w4(wq, s), threads=CORES)
+    assert_bar(bf16_to_f32(out[torch.from_numpy(rows).cuda()]), ref, K, "prefill 4096^3 rows")
+
+
 def test_w4a16_is_deterministic():
     import cudaop_b200 as ops
     xb, wq, s = oracle.make_w4a16_case(16, 4096, 4096, seed=5)
