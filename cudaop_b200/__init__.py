@@ -69,6 +69,7 @@ _SIGNATURES = {
     "b200q_status": [_VP, _I],
     "b200q_set_wait_limit_ms": [_I, _I],
     "b200q_rank_barrier": [_VP, _I, _I, C.c_uint, C.c_uint, _VP],
+    "b200q_reduce_scatter_to_bf16_one_device": [_VP, _VP, _VP, _I, C.c_longlong, C.c_longlong, _I, C.c_uint, C.c_uint, _I, _VP],
     "b200q_allreduce_to_bf16_one_device": [_VP, _VP, _VP, _I, C.c_longlong, C.c_longlong, _I, C.c_uint, C.c_uint, _I, _VP],
     "b200q_gemm_fp8_rowcol_allreduce_one_device": [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I,
                                                    C.c_uint, C.c_uint, _I, _I, _VP],

@@ -108,12 +108,12 @@ reduce_scatter_to_bf16_kernel(const Params p)
 // that rank's buffers (all in this device's memory).  The launch is cooperative, so all CTAs are resident at
 // once and the flag protocol between the "ranks" makes progress; separate launches that wait on one another
 // on one device would have no such guarantee.  Peer loads/stores only.
-template <bool PartialBf16>
+template <bool PartialBf16, bool SCATTER>
 __global__ void __launch_bounds__(kThreads)
 allreduce_one_device_kernel(Params p, int ctas_per_rank)
 {
     p.rank = blockIdx.x / ctas_per_rank;
-    allreduce_body<false, PartialBf16, 2>(p, blockIdx.x % ctas_per_rank, ctas_per_rank);
+    allreduce_body<false, PartialBf16, 2, SCATTER>(p, blockIdx.x % ctas_per_rank, ctas_per_rank);
 }
 
 // One tiny CTA: a barrier over all ranks on the launching streams (bounded like every other wait).
@@ -205,10 +205,10 @@ int b200q_reduce_scatter_to_bf16(const void* const* partial_ptrs_dev, void* cons
     return cudaGetLastError();
 }
 
-int b200q_allreduce_to_bf16_one_device(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
-                                       void* const* signal_ptrs_dev, int partial_is_bf16, long long elem_offset,
-                                       long long elems, int world, unsigned int epoch, unsigned int signal_offset_bytes,
-                                       int ctas_per_rank, void* stream)
+namespace {
+int one_device(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev, void* const* signal_ptrs_dev,
+               int partial_is_bf16, long long elem_offset, long long elems, int world, unsigned int epoch,
+               unsigned int signal_offset_bytes, int ctas_per_rank, bool scatter, void* stream)
 {
     using namespace b200q;
     if (partial_ptrs_dev == nullptr || out_ptrs_dev == nullptr || signal_ptrs_dev == nullptr) return cudaErrorInvalidValue;
@@ -224,10 +224,32 @@ int b200q_allreduce_to_bf16_one_device(const void* const* partial_ptrs_dev, void
     p.status = status_ptr();
     if (p.status == nullptr) return cudaErrorInvalidDevice;
     void* args[2] = {&p, &ctas_per_rank};
-    const void* fn = partial_is_bf16 ? reinterpret_cast<const void*>(ar::allreduce_one_device_kernel<true>)
-                                     : reinterpret_cast<const void*>(ar::allreduce_one_device_kernel<false>);
+    const void* fn = scatter
+        ? (partial_is_bf16 ? reinterpret_cast<const void*>(ar::allreduce_one_device_kernel<true, true>)
+                           : reinterpret_cast<const void*>(ar::allreduce_one_device_kernel<false, true>))
+        : (partial_is_bf16 ? reinterpret_cast<const void*>(ar::allreduce_one_device_kernel<true, false>)
+                           : reinterpret_cast<const void*>(ar::allreduce_one_device_kernel<false, false>));
     // cooperative: refused with cudaErrorCooperativeLaunchTooLarge when the CTAs cannot all be resident
     return cudaLaunchCooperativeKernel(fn, dim3(world * ctas_per_rank), dim3(128), args, 0, static_cast<cudaStream_t>(stream));
+}
+}  // namespace
+
+int b200q_allreduce_to_bf16_one_device(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                       void* const* signal_ptrs_dev, int partial_is_bf16, long long elem_offset,
+                                       long long elems, int world, unsigned int epoch, unsigned int signal_offset_bytes,
+                                       int ctas_per_rank, void* stream)
+{
+    return one_device(partial_ptrs_dev, out_ptrs_dev, signal_ptrs_dev, partial_is_bf16, elem_offset, elems, world, epoch,
+                      signal_offset_bytes, ctas_per_rank, false, stream);
+}
+
+int b200q_reduce_scatter_to_bf16_one_device(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                            void* const* signal_ptrs_dev, int partial_is_bf16, long long elem_offset,
+                                            long long elems, int world, unsigned int epoch,
+                                            unsigned int signal_offset_bytes, int ctas_per_rank, void* stream)
+{
+    return one_device(partial_ptrs_dev, out_ptrs_dev, signal_ptrs_dev, partial_is_bf16, elem_offset, elems, world, epoch,
+                      signal_offset_bytes, ctas_per_rank, true, stream);
 }
 
 size_t b200q_rank_barrier_signal_bytes(void) { return static_cast<size_t>(b200q::ar::kMaxWorld) * sizeof(uint32_t); }

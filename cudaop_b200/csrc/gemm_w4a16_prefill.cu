@@ -44,6 +44,14 @@ constexpr int kAccStride = 160;                    // columns between the two ac
 constexpr int kSmemBytes = kStages * kStageBytes + kScaleBytes + 1024 + 256;
 static_assert(kStageBytes % 1024 == 0 && (kXBytes + kWpBytes) % 1024 == 0, "operand tiles start 1024-byte aligned");
 
+// (136 + q, 136 + q') as bf16x2 -> (q, q'): exact, both sides are integers below 256
+__device__ __forceinline__ uint32_t sub136(uint32_t v)
+{
+    const uint32_t k = 0x43084308u;
+    const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v), *reinterpret_cast<const __nv_bfloat162*>(&k));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
 struct Params {
     const __half* S;
     __nv_bfloat16* Y;
@@ -52,6 +60,10 @@ struct Params {
     uint32_t* status;
 };
 
+// SUB: the converters subtract the offset again (one exact bf16x2 subtraction per pair: 136 + q and q are both
+// bf16 integers), the B tile holds q itself, no rows of ones are multiplied and the fold is one fused
+// multiply-add per value.
+template <bool SUB>
 __global__ void __launch_bounds__(kThreads, 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const Params p)
 {
@@ -84,7 +96,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         ptx::fence_mbar_init();
     }
     // rows 128..143 of every stage's B tile: bf16 1.0 in every K position (the swizzle permutes equal chunks)
-    for (int i = threadIdx.x; i < kStages * 16 * 8; i += kThreads) {
+    for (int i = threadIdx.x; i < (SUB ? 0 : kStages * 16 * 8); i += kThreads) {
         const int s = i / 128, r = (i >> 3) & 15, c = i & 7;
         ptx::st_shared_v4(wb_tile(s) + (kBN + r) * 128 + c * 16, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
     }
@@ -116,7 +128,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
         if (ptx::elect_one()) {
-            constexpr uint32_t idesc = ptx::umma_idesc(1 /*bf16*/, 1 /*bf16*/, kBM, kBNmma);
+            constexpr uint32_t idesc = ptx::umma_idesc(1 /*bf16*/, 1 /*bf16*/, kBM, SUB ? kBN : kBNmma);
             int stage = 0; uint32_t phase = 0; bool ok = true;
             int gi = 0;                                             // groups issued so far (over all tiles)
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
@@ -167,8 +179,8 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                 if (!ptx::mbar_wait(tfull_bar(buf), (gi >> 1) & 1u, p.status, 35)) { ok = false; break; }
                 ptx::tcgen05_fence_after_sync();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kAccStride;
-                uint32_t ones[8];
-                ptx::tmem_ld_32x32b_x8(taddr + kBN, ones);       // sum over the group of this token's activations
+                uint32_t ones[8] = {};
+                if (!SUB) ptx::tmem_ld_32x32b_x8(taddr + kBN, ones);   // sum over the group of this token's activations
                 float t = 0.0f;
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {                    // sixteen weight rows at a time: registers are the scarce resource
@@ -177,13 +189,18 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                     const uint4 s0 = *reinterpret_cast<const uint4*>(sc_sm + g * kBN + 64 * half + 16 * c);
                     const uint4 s1 = *reinterpret_cast<const uint4*>(sc_sm + g * kBN + 64 * half + 16 * c + 8);
                     ptx::tmem_ld_wait();
-                    if (c == 0) t = -136.0f * __uint_as_float(ones[0]);
+                    if (!SUB && c == 0) t = -136.0f * __uint_as_float(ones[0]);
                     const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const float2 sc2 = __half22float2(*reinterpret_cast<const __half2*>(&sw[i]));
-                        acc[16 * c + 2 * i] = fmaf(__uint_as_float(d[2 * i]) + t, sc2.x, acc[16 * c + 2 * i]);
-                        acc[16 * c + 2 * i + 1] = fmaf(__uint_as_float(d[2 * i + 1]) + t, sc2.y, acc[16 * c + 2 * i + 1]);
+                        if (SUB) {
+                            acc[16 * c + 2 * i] = fmaf(__uint_as_float(d[2 * i]), sc2.x, acc[16 * c + 2 * i]);
+                            acc[16 * c + 2 * i + 1] = fmaf(__uint_as_float(d[2 * i + 1]), sc2.y, acc[16 * c + 2 * i + 1]);
+                        } else {
+                            acc[16 * c + 2 * i] = fmaf(__uint_as_float(d[2 * i]) + t, sc2.x, acc[16 * c + 2 * i]);
+                            acc[16 * c + 2 * i + 1] = fmaf(__uint_as_float(d[2 * i + 1]) + t, sc2.y, acc[16 * c + 2 * i + 1]);
+                        }
                     }
                 }
                 ptx::tcgen05_fence_before_sync();
@@ -224,10 +241,11 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                 for (int j = 0; j < 8; ++j) {                      // word j: K offsets 8 j .. 8 j + 7 of this stage
                     // nibble pairs (i, i + 4) as bf16 integers 128 + (q + 8): (w & mask) ^ const does the sign flip and
                     // the exponent in one logic operation; then pairs of ascending K by byte permutes
-                    const uint32_t a0 = (ww[j] & 0x000F000Fu) ^ 0x43084308u;
-                    const uint32_t a1 = ((ww[j] >> 4) & 0x000F000Fu) ^ 0x43084308u;
-                    const uint32_t a2 = ((ww[j] >> 8) & 0x000F000Fu) ^ 0x43084308u;
-                    const uint32_t a3 = ((ww[j] >> 12) & 0x000F000Fu) ^ 0x43084308u;
+                    uint32_t a0 = (ww[j] & 0x000F000Fu) ^ 0x43084308u;
+                    uint32_t a1 = ((ww[j] >> 4) & 0x000F000Fu) ^ 0x43084308u;
+                    uint32_t a2 = ((ww[j] >> 8) & 0x000F000Fu) ^ 0x43084308u;
+                    uint32_t a3 = ((ww[j] >> 12) & 0x000F000Fu) ^ 0x43084308u;
+                    if (SUB) { a0 = sub136(a0); a1 = sub136(a1); a2 = sub136(a2); a3 = sub136(a3); }
                     const int chunk = j ^ (r & 7);                 // 16-byte unit inside the 128-byte row, 128-byte swizzle
                     ptx::st_shared_v4(wb_tile(stage) + r * 128 + chunk * 16, __byte_perm(a0, a1, 0x5410), __byte_perm(a2, a3, 0x5410),
                                       __byte_perm(a0, a1, 0x7632), __byte_perm(a2, a3, 0x7632));
@@ -254,7 +272,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 namespace b200q {
 
 // Called by b200q_gemm_w4a16 for more than 16 tokens (K a multiple of 128, at most 16384).
-int gemm_w4a16_prefill(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, void* stream)
+int gemm_w4a16_prefill(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, int sub, void* stream)
 {
     using namespace w4p;
     if (X == nullptr || Wq == nullptr || S == nullptr || Y == nullptr) return cudaErrorInvalidValue;
@@ -280,14 +298,18 @@ int gemm_w4a16_prefill(const void* X, const void* Wq, const void* S, void* Y, in
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(w4a16_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        e = cudaFuncSetAttribute(w4a16_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(w4a16_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
     const int sms = num_sms();
     if (sms <= 0) return cudaErrorInvalidDevice;
     const int tiles = p.tiles_m * p.tiles_n;
-    w4a16_prefill_kernel<<<tiles < sms ? tiles : sms, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmW, p);
+    const int grid = tiles < sms ? tiles : sms;
+    if (sub) w4a16_prefill_kernel<true><<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmW, p);
+    else w4a16_prefill_kernel<false><<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmW, p);
     return cudaGetLastError();
 }
 

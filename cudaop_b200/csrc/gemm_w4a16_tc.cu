@@ -343,7 +343,7 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
 
 int g_impl = 0;      // 0 = by M: streaming GEMV (gemm_w4a16_stream.cu; the older GEMV forms of gemm_w4a16_gemv.cu when K does not suit it)
                      // for one token, the prefill kernel (gemm_w4a16_prefill.cu) above 16 tokens, else the warp-MMA kernel (gemm_w4a16.cu);
-                     // 5 = the streaming GEMV where it applies; 6 = the prefill kernel for every M;
+                     // 5 = the streaming GEMV where it applies; 6 / 7 = the prefill kernel for every M (offset taken out by rows of ones / by the converters);
                      // 1 = tcgen05 kernel (this file); 2 = warp-MMA kernel for every M; 3 / 4 = GEMV up to 4 tokens, weights
                      // through shared memory (dp4a arithmetic) / in registers (fp32 arithmetic)
 int g_pdl = 0;       // programmatic dependent launch (b200q_w4a16_set_pdl) of the GEMV and tcgen05 kernels, off by default
@@ -361,12 +361,12 @@ int gemm_w4a16_gemv(const void* X, const void* Wq, const void* S, void* Y, int M
 // gemm_w4a16_stream.cu: one token, fat CTAs that prefetch their whole weight block (K % 2048 == 0, K <= 16384)
 int gemm_w4a16_stream(const void* X, const void* Wq, const void* S, void* Y, int N, int K, int group, int pdl, void* stream);
 // gemm_w4a16_prefill.cu: many tokens, tcgen05 with group-wise partial-sum scaling (K % 128 == 0, K <= 16384)
-int gemm_w4a16_prefill(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, void* stream);
+int gemm_w4a16_prefill(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, int sub, void* stream);
 }
 
 extern "C" int b200q_w4a16_set_impl(int impl)
 {
-    if (impl < 0 || impl > 6) return cudaErrorInvalidValue;
+    if (impl < 0 || impl > 7) return cudaErrorInvalidValue;
     b200q::w4tc::g_impl = impl;
     return 0;
 }
@@ -381,8 +381,8 @@ extern "C" int b200q_gemm_w4a16(const void* X, const void* Wq, const void* S, vo
                                 void* stream)
 {
     using namespace b200q;
-    if (((M > 16 && w4tc::g_impl == 0) || w4tc::g_impl == 6) && group == 128 && K > 0 && K % 128 == 0 && K <= 16384)
-        return gemm_w4a16_prefill(X, Wq, S, Y, M, N, K, group, stream);
+    if (((M > 16 && w4tc::g_impl == 0) || w4tc::g_impl == 6 || w4tc::g_impl == 7) && group == 128 && K > 0 && K % 128 == 0 && K <= 16384)
+        return gemm_w4a16_prefill(X, Wq, S, Y, M, N, K, group, w4tc::g_impl == 7 ? 1 : 0, stream);
     if (M == 1 && (w4tc::g_impl == 0 || w4tc::g_impl == 5) && group == 128 && K > 0 && K % 2048 == 0 && K <= 16384)
         return gemm_w4a16_stream(X, Wq, S, Y, N, K, group, w4tc::g_pdl, stream);
     if (M == 1 && (w4tc::g_impl == 0 || w4tc::g_impl == 5)) {

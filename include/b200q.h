@@ -156,7 +156,8 @@ int b200q_nvfp4_set_2cta(int on);      /* NVFP4 GEMM on CTA pairs (256 x 192 / 2
 int b200q_w4a16_set_impl(int impl);     /* 0 = by M (default): streaming CUDA-core GEMV for one token (the older GEMV forms when K is not
                                          * a multiple of 2048 or exceeds 16384), warp-MMA kernel for 2..16 tokens, tcgen05
                                          * prefill kernel (group-wise partial-sum scaling) above 16; 5 / 6 = the streaming
-                                         * GEMV / the prefill kernel wherever they apply;
+                                         * GEMV / the prefill kernel wherever they apply; 7 = the prefill kernel whose
+                                         * converters subtract the integer offset themselves;
                                          * 1 = tcgen05 kernel; 2 = warp-MMA kernel for every M; 3 / 4 = the two GEMV forms
                                          * (shared memory + dp4a / registers + fp32) for up to 4 tokens */
 int b200q_w4a16_set_pdl(int on);        /* programmatic dependent launch of the GEMV / tcgen05 W4A16 kernels (default off):
@@ -242,6 +243,12 @@ int b200q_allreduce_to_bf16_one_device(const void* const* partial_ptrs_dev, void
                                        void* const* signal_ptrs_dev, int partial_is_bf16, long long elem_offset,
                                        long long elems, int world, unsigned int epoch, unsigned int signal_offset_bytes,
                                        int ctas_per_rank, void* stream);
+/* The reduce-scatter half in the same one-launch form: "rank" r's CTAs write elements
+ * [elem_offset + r * elems / world, elem_offset + (r + 1) * elems / world) of the sum to out_ptrs_dev[r] only. */
+int b200q_reduce_scatter_to_bf16_one_device(const void* const* partial_ptrs_dev, void* const* out_ptrs_dev,
+                                            void* const* signal_ptrs_dev, int partial_is_bf16, long long elem_offset,
+                                            long long elems, int world, unsigned int epoch,
+                                            unsigned int signal_offset_bytes, int ctas_per_rank, void* stream);
 /* The same for b200q_gemm_fp8_rowcol_allreduce (world <= 4).  A_host / B_host / row_scale_host / partial_host /
  * counters_host are HOST arrays of `world` device pointers (rank r's operands, its partial buffer = entry r of
  * partial_ptrs_dev, its counter block); col_scale is shared; the three *_dev tables are device arrays. */

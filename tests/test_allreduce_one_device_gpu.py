@@ -60,6 +60,50 @@ def test_allreduce_kernel_all_ranks_in_one_launch(world, pdt):
 
 
 @pytest.mark.parametrize("pdt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("world", [2, 4])
+def test_reduce_scatter_kernel_all_ranks_in_one_launch(world, pdt):
+    """The reduce-scatter half: rank r's output holds its 1/world of the sum and nothing else is touched."""
+    import cudaop_b200 as ops
+    L = ops.lib()
+    g = torch.Generator(device="cuda").manual_seed(200 + world)
+    elems = 8 * world * 1531
+    per = elems // world
+    parts = [torch.randn(elems, device="cuda", generator=g).to(pdt) for _ in range(world)]
+    outs = [torch.full((elems,), -7.0, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(L.b200q_allreduce_signal_bytes() // 4, dtype=torch.int32, device="cuda") for _ in range(world)]
+    tp, to, tf = _ptr_table(parts), _ptr_table(outs), _ptr_table(flags)
+    st = torch.cuda.current_stream().cuda_stream
+    want = _rank_order_sum(parts)
+    for epoch in (1, 2):
+        rc = L.b200q_reduce_scatter_to_bf16_one_device(tp.data_ptr(), to.data_ptr(), tf.data_ptr(), int(pdt == torch.bfloat16),
+                                                       0, elems, world, epoch, 0, 3, st)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert ops.status() == 0
+        for r, o in enumerate(outs):
+            assert torch.equal(o[r * per:(r + 1) * per], want[r * per:(r + 1) * per])
+            rest = torch.cat([o[:r * per], o[(r + 1) * per:]])
+            assert bool((rest == -7.0).all())
+
+
+def test_reduce_scatter_one_rank_world():
+    """world = 1 through the per-rank entry point: the rank's own partial, rounded once."""
+    import cudaop_b200 as ops
+    L = ops.lib()
+    elems = 8 * 4099
+    part = torch.randn(elems, device="cuda")
+    out = torch.zeros(elems, dtype=torch.bfloat16, device="cuda")
+    flags = torch.zeros(L.b200q_allreduce_signal_bytes() // 4, dtype=torch.int32, device="cuda")
+    tp, to, tf = _ptr_table([part]), _ptr_table([out]), _ptr_table([flags])
+    rc = L.b200q_reduce_scatter_to_bf16(tp.data_ptr(), to.data_ptr(), tf.data_ptr(), None, 0, 0, elems, 0, 1, 1, 0, 4,
+                                        torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert ops.status() == 0
+    assert torch.equal(out, part.to(torch.bfloat16))
+
+
+@pytest.mark.parametrize("pdt", [torch.bfloat16, torch.float32])
 def test_fused_down_projection_allreduce_all_ranks_in_one_launch(pdt):
     import cudaop_b200 as ops
     L = ops.lib()

@@ -100,14 +100,16 @@ def test_one_token_streaming_form_propagates_non_finite_activations(impl):
 
 @pytest.mark.parametrize("shape", [(17, 128, 128), (64, 256, 256), (200, 130, 1152), (129, 1000, 384), (512, 4096, 4096),
                                    (300, 72, 16384), (2, 40, 256)])
-def test_prefill_form(shape, impl):
+@pytest.mark.parametrize("form", [6, 7])
+def test_prefill_form(shape, form, impl):
     """The tcgen05 prefill kernel (integer weights on the tensor core, the group's scale applied to its fp32 partial
-    sum): ragged token and row counts, one to 128 groups; every output against the oracle."""
+    sum), in both of its forms (6: the converters leave the offset 136 in and sixteen rows of ones take it out; 7: the
+    converters subtract it): ragged token and row counts, one to 128 groups; every output against the oracle."""
     import cudaop_b200 as ops
     if impl != (0, 0):
         pytest.skip("selects its own implementation")
     M, N, K = shape
-    ops.lib().b200q_w4a16_set_impl(6)
+    ops.lib().b200q_w4a16_set_impl(form)
     xb, wq, s = oracle.make_w4a16_case(M, N, K, seed=M + N + K)
     out = ops.gemm_w4a16(dev(xb, torch.bfloat16), dev(wq), dev(s, torch.float16))
     torch.cuda.synchronize()
