@@ -30,19 +30,21 @@ constexpr int kBN = 128;             // weight rows per tile
 constexpr int kBNmma = kBN + 16;     // + sixteen rows of ones (UMMA N, a multiple of 16)
 constexpr int kGroup = 128;          // K per scale group
 constexpr int kBK = 64;              // K per pipeline stage: one 128-byte swizzle row of bf16; two stages per group
-constexpr int kStages = 4;
+constexpr int kMaxLoadStages = 12;   // ring of TMA destinations (activations + packed weights); its depth is set per launch
+constexpr int kMaxWbStages = 4;      // ring of converted weight tiles
 constexpr int kMaxGroups = 128;      // scales of a tile are staged in shared memory: K <= 16384
 constexpr int kXBytes = kBM * 128;                 // 16 KiB
 constexpr int kWpBytes = kBN * 32;                 // packed weights of a stage, 4 KiB
 constexpr int kWbBytes = kBNmma * 128;             // converted weights, 18 KiB
-constexpr int kStageBytes = kXBytes + kWpBytes + kWbBytes;     // 38 KiB, a multiple of 1024
-constexpr int kScaleBytes = kMaxGroups * kBN * 2;  // [group][row] fp16
-constexpr int kFoldWarps = 8, kConvWarps = 4;
+constexpr int kLoadBytes = kXBytes + kWpBytes;     // 20 KiB per load stage
+
+constexpr int kFoldWarps = 8, kConvWarps = 4;     // converter warps per team; one team converts a stage
 constexpr int kThreads = 32 * (2 + kFoldWarps + kConvWarps);
 constexpr uint32_t kTmemCols = 512;                // two accumulators of 144 columns (allocations are powers of two)
 constexpr int kAccStride = 160;                    // columns between the two accumulators
-constexpr int kSmemBytes = kStages * kStageBytes + kScaleBytes + 1024 + 256;
-static_assert(kStageBytes % 1024 == 0 && (kXBytes + kWpBytes) % 1024 == 0, "operand tiles start 1024-byte aligned");
+constexpr int kBarBytes = 512;
+constexpr int kMaxSmemBytes = 232448;              // 227 KiB per CTA
+static_assert(kXBytes % 1024 == 0 && kWpBytes % 1024 == 0 && kWbBytes % 1024 == 0, "operand tiles start 1024-byte aligned");
 
 // (136 + q, 136 + q') as bf16x2 -> (q, q'): exact, both sides are integers below 256
 __device__ __forceinline__ uint32_t sub136(uint32_t v)
@@ -57,46 +59,53 @@ struct Params {
     __nv_bfloat16* Y;
     int M, N, K;
     int tiles_m, tiles_n;
+    int load_stages;      // depth of the TMA ring: as deep as shared memory allows beside the scales of K / 128 groups
+    int dbg;
     uint32_t* status;
 };
 
 // SUB: the converters subtract the offset again (one exact bf16x2 subtraction per pair: 136 + q and q are both
 // bf16 integers), the B tile holds q itself, no rows of ones are multiplied and the fold is one fused
 // multiply-add per value.
-template <bool SUB>
-__global__ void __launch_bounds__(kThreads, 1)
+// TEAMS: teams of four converter warps; team t converts the stages whose running index is t modulo TEAMS.
+// WIDE: the fold reads 32 accumulator columns per tcgen05.ld (two round trips per group instead of four).
+// dbg (measurement only): bit 0 = converters write nothing, bit 1 = the fold adds nothing.
+template <bool SUB, int TEAMS, bool WIDE>
+__global__ void __launch_bounds__(kThreads + 32 * kConvWarps * (TEAMS - 1), 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-    auto x_tile = [&](int s) { return smem_base + s * kStageBytes; };
-    auto wp_tile = [&](int s) { return smem_base + s * kStageBytes + kXBytes; };
-    auto wb_tile = [&](int s) { return smem_base + s * kStageBytes + kXBytes + kWpBytes; };
-    const uint32_t scale_base = smem_base + kStages * kStageBytes;             // [group][128 rows] fp16
-    const uint32_t bar_base = scale_base + kScaleBytes;
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };                   // X and packed W of the stage have landed
-    auto conv_bar = [&](int s) { return bar_base + 8u * (kStages + s); };       // the stage's bf16 weights are written
-    auto empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };  // the stage's MMAs have retired
-    auto tfull_bar = [&](int b) { return bar_base + 8u * (3 * kStages + b); };
-    auto tempty_bar = [&](int b) { return bar_base + 8u * (3 * kStages + 2 + b); };
-    const uint32_t tmem_slot = bar_base + 8u * (3 * kStages + 4);
+    constexpr int kWS = TEAMS > 1 ? 4 : 3;                  // converted tiles in flight
+    const int LS = p.load_stages;
+    const int G = p.K / kGroup;
+    auto x_tile = [&](int s) { return smem_base + s * kXBytes; };
+    auto wp_tile = [&](int s) { return smem_base + LS * kXBytes + s * kWpBytes; };
+    auto wb_tile = [&](int w) { return smem_base + LS * kLoadBytes + w * kWbBytes; };
+    const uint32_t scale_base = smem_base + LS * kLoadBytes + kWS * kWbBytes;  // [group][128 rows] fp16
+    const uint32_t bar_base = scale_base + G * kBN * 2;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };                            // X and packed W have landed
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxLoadStages + s); };        // the MMAs that read X have retired
+    auto conv_bar = [&](int w) { return bar_base + 8u * (2 * kMaxLoadStages + w); };     // the bf16 weights are written
+    auto wfree_bar = [&](int w) { return bar_base + 8u * (2 * kMaxLoadStages + kMaxWbStages + w); };   // ... and read
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kMaxLoadStages + 2 * kMaxWbStages + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxLoadStages + 2 * kMaxWbStages + 2 + b); };
+    const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxLoadStages + 2 * kMaxWbStages + 4);
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int G = p.K / kGroup;
     const int stages_per_tile = p.K / kBK;                  // two per group
     const int num_tiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
-            ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(conv_bar(s), kConvWarps); ptx::mbar_init(empty_bar(s), 1);
-        }
+        for (int s = 0; s < LS; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
+        for (int w = 0; w < kWS; ++w) { ptx::mbar_init(conv_bar(w), kConvWarps); ptx::mbar_init(wfree_bar(w), 1); }
         for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull_bar(b), 1); ptx::mbar_init(tempty_bar(b), kFoldWarps); }
         ptx::fence_mbar_init();
     }
     // rows 128..143 of every stage's B tile: bf16 1.0 in every K position (the swizzle permutes equal chunks)
-    for (int i = threadIdx.x; i < (SUB ? 0 : kStages * 16 * 8); i += kThreads) {
+    for (int i = threadIdx.x; i < (SUB ? 0 : kWS * 16 * 8); i += blockDim.x) {
         const int s = i / 128, r = (i >> 3) & 15, c = i & 7;
         ptx::st_shared_v4(wb_tile(s) + (kBN + r) * 128 + c * 16, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u, 0x3F803F80u);
     }
@@ -120,7 +129,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                     ptx::mbar_arrive_expect_tx(full_bar(stage), kXBytes + kWpBytes);
                     ptx::tma_load_2d(x_tile(stage), &tmX, full_bar(stage), i * kBK, m0);          // x counts bf16 elements
                     ptx::tma_load_2d(wp_tile(stage), &tmW, full_bar(stage), i * (kBK / 2), n0);   // x counts bytes
-                    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                    if (++stage == LS) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok) __nanosleep(200000);
@@ -130,6 +139,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         if (ptx::elect_one()) {
             constexpr uint32_t idesc = ptx::umma_idesc(1 /*bf16*/, 1 /*bf16*/, kBM, SUB ? kBN : kBNmma);
             int stage = 0; uint32_t phase = 0; bool ok = true;
+            int wst = 0; uint32_t wphase = 0;                       // position in the ring of converted tiles
             int gi = 0;                                             // groups issued so far (over all tiles)
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 for (int g = 0; g < G && ok; ++g, ++gi) {
@@ -139,14 +149,16 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                     const uint32_t d_tmem = tmem_base + buf * kAccStride;
                     for (int h = 0; h < 2; ++h) {
                         if (!ptx::mbar_wait(full_bar(stage), phase, p.status, 33) ||
-                            !ptx::mbar_wait(conv_bar(stage), phase, p.status, 34)) { ok = false; break; }
+                            !ptx::mbar_wait(conv_bar(wst), wphase, p.status, 34)) { ok = false; break; }
                         ptx::tcgen05_fence_after_sync();
-                        const uint64_t da = ptx::smem_desc_sw128_kmajor(x_tile(stage)), db = ptx::smem_desc_sw128_kmajor(wb_tile(stage));
+                        const uint64_t da = ptx::smem_desc_sw128_kmajor(x_tile(stage)), db = ptx::smem_desc_sw128_kmajor(wb_tile(wst));
 #pragma unroll
                         for (int k = 0; k < kBK / 16; ++k)          // 16 K = 32 bytes per instruction: +2 in 16-byte units
                             ptx::umma_f16(d_tmem, da + 2u * k, db + 2u * k, idesc, (h | k) != 0);
                         ptx::umma_commit(empty_bar(stage));
-                        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                        ptx::umma_commit(wfree_bar(wst));
+                        if (++stage == LS) { stage = 0; phase ^= 1u; }
+                        if (++wst == kWS) { wst = 0; wphase ^= 1u; }
                     }
                     if (ok) ptx::umma_commit(tfull_bar(buf));
                 }
@@ -182,24 +194,31 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                 uint32_t ones[8] = {};
                 if (!SUB) ptx::tmem_ld_32x32b_x8(taddr + kBN, ones);   // sum over the group of this token's activations
                 float t = 0.0f;
+                constexpr int kCols = WIDE ? 32 : 16;                  // accumulator columns per tcgen05.ld
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {                    // sixteen weight rows at a time: registers are the scarce resource
-                    uint32_t d[16];
-                    ptx::tmem_ld_32x32b_x16(taddr + 64 * half + 16 * c, d);
-                    const uint4 s0 = *reinterpret_cast<const uint4*>(sc_sm + g * kBN + 64 * half + 16 * c);
-                    const uint4 s1 = *reinterpret_cast<const uint4*>(sc_sm + g * kBN + 64 * half + 16 * c + 8);
+                for (int c = 0; c < 64 / kCols; ++c) {                 // registers are the scarce resource
+                    uint32_t d[kCols];
+                    ptx::tmem_ld_32x32b<kCols>(taddr + 64 * half + kCols * c, d);
+                    uint32_t sw[kCols / 2];
+#pragma unroll
+                    for (int v = 0; v < kCols / 8; ++v) {
+                        const uint4 sv = *reinterpret_cast<const uint4*>(sc_sm + g * kBN + 64 * half + kCols * c + 8 * v);
+                        sw[4 * v] = sv.x; sw[4 * v + 1] = sv.y; sw[4 * v + 2] = sv.z; sw[4 * v + 3] = sv.w;
+                    }
                     ptx::tmem_ld_wait();
                     if (!SUB && c == 0) t = -136.0f * __uint_as_float(ones[0]);
-                    const uint32_t sw[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                    if (p.dbg & 2) continue;
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
+                    for (int i = 0; i < kCols / 2; ++i) {
                         const float2 sc2 = __half22float2(*reinterpret_cast<const __half2*>(&sw[i]));
+                        float& a0 = acc[kCols * c + 2 * i];
+                        float& a1 = acc[kCols * c + 2 * i + 1];
                         if (SUB) {
-                            acc[16 * c + 2 * i] = fmaf(__uint_as_float(d[2 * i]), sc2.x, acc[16 * c + 2 * i]);
-                            acc[16 * c + 2 * i + 1] = fmaf(__uint_as_float(d[2 * i + 1]), sc2.y, acc[16 * c + 2 * i + 1]);
+                            a0 = fmaf(__uint_as_float(d[2 * i]), sc2.x, a0);
+                            a1 = fmaf(__uint_as_float(d[2 * i + 1]), sc2.y, a1);
                         } else {
-                            acc[16 * c + 2 * i] = fmaf(__uint_as_float(d[2 * i]) + t, sc2.x, acc[16 * c + 2 * i]);
-                            acc[16 * c + 2 * i + 1] = fmaf(__uint_as_float(d[2 * i + 1]) + t, sc2.y, acc[16 * c + 2 * i + 1]);
+                            a0 = fmaf(__uint_as_float(d[2 * i]) + t, sc2.x, a0);
+                            a1 = fmaf(__uint_as_float(d[2 * i + 1]) + t, sc2.y, a1);
                         }
                     }
                 }
@@ -229,16 +248,26 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         }
     } else {
         // ---------------------------------------------------------------- converters: packed int4 -> bf16 B tile
-        const int r = threadIdx.x - 32 * (2 + kFoldWarps);       // 0..127: the weight row this thread converts
+        const int ct = threadIdx.x - 32 * (2 + kFoldWarps);
+        const int r = ct & 127;                                  // the weight row this thread converts
+        const int team = ct >> 7;
         int stage = 0; uint32_t phase = 0; bool ok = true;
+        int wst = 0; uint32_t wphase = 0;
+        int it = 0;                                              // running stage index over all tiles
+        auto advance = [&]() {
+            if (++stage == LS) { stage = 0; phase ^= 1u; }
+            if (++wst == kWS) { wst = 0; wphase ^= 1u; }
+        };
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            for (int i = 0; i < stages_per_tile; ++i) {
-                if (!ptx::mbar_wait(full_bar(stage), phase, p.status, 36)) { ok = false; break; }
+            for (int i = 0; i < stages_per_tile; ++i, ++it) {
+                if (TEAMS > 1 && (it % TEAMS) != team) { advance(); continue; }
+                if (!ptx::mbar_wait(full_bar(stage), phase, p.status, 36) ||
+                    !ptx::mbar_wait(wfree_bar(wst), wphase ^ 1u, p.status, 37)) { ok = false; break; }
                 const uint4* wrow = reinterpret_cast<const uint4*>(smem_gen + (wp_tile(stage) - smem_base) + 32 * r);
                 const uint4 w0 = wrow[0], w1 = wrow[1];
                 const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {                      // word j: K offsets 8 j .. 8 j + 7 of this stage
+                for (int j = 0; j < ((p.dbg & 1) ? 0 : 8); ++j) {  // word j: K offsets 8 j .. 8 j + 7 of this stage
                     // nibble pairs (i, i + 4) as bf16 integers 128 + (q + 8): (w & mask) ^ const does the sign flip and
                     // the exponent in one logic operation; then pairs of ascending K by byte permutes
                     uint32_t a0 = (ww[j] & 0x000F000Fu) ^ 0x43084308u;
@@ -247,13 +276,13 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                     uint32_t a3 = ((ww[j] >> 12) & 0x000F000Fu) ^ 0x43084308u;
                     if (SUB) { a0 = sub136(a0); a1 = sub136(a1); a2 = sub136(a2); a3 = sub136(a3); }
                     const int chunk = j ^ (r & 7);                 // 16-byte unit inside the 128-byte row, 128-byte swizzle
-                    ptx::st_shared_v4(wb_tile(stage) + r * 128 + chunk * 16, __byte_perm(a0, a1, 0x5410), __byte_perm(a2, a3, 0x5410),
+                    ptx::st_shared_v4(wb_tile(wst) + r * 128 + chunk * 16, __byte_perm(a0, a1, 0x5410), __byte_perm(a2, a3, 0x5410),
                                       __byte_perm(a0, a1, 0x7632), __byte_perm(a2, a3, 0x7632));
                 }
                 ptx::fence_proxy_async_smem();                     // the MMA reads these ordinary stores through the async proxy
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(conv_bar(stage));
-                if (++stage == kStages) { stage = 0; phase ^= 1u; }
+                if (lane == 0) ptx::mbar_arrive(conv_bar(wst));
+                advance();
             }
         }
     }
@@ -270,6 +299,13 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 }  // namespace b200q
 
 namespace b200q {
+
+int g_prefill_variant = 0, g_prefill_dbg = 0, g_prefill_depth = 0;
+extern "C" int b200q_w4a16_prefill_debug(int variant, int dbg, int depth)
+{
+    g_prefill_variant = variant; g_prefill_dbg = dbg; g_prefill_depth = depth;
+    return 0;
+}
 
 // Called by b200q_gemm_w4a16 for more than 16 tokens (K a multiple of 128, at most 16384).
 int gemm_w4a16_prefill(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, int sub, void* stream)
@@ -293,23 +329,29 @@ int gemm_w4a16_prefill(const void* X, const void* Wq, const void* S, void* Y, in
             return cudaErrorInvalidValue;
     }
     if (!make_tmap_2d_u8(&tmW, Wq, N, K / 2, K / 2, kBN, kBK / 2, CU_TENSOR_MAP_SWIZZLE_NONE)) return cudaErrorInvalidValue;
-    static bool configured[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    if (dev < 64 && !configured[dev]) {
-        e = cudaFuncSetAttribute(w4a16_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(w4a16_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured[dev] = true;
-    }
+    p.dbg = g_prefill_dbg;
+    const int teams = g_prefill_variant == 2 ? 2 : 1;
+    const int fixed = 1024 + kBarBytes + (teams > 1 ? 4 : 3) * kWbBytes + (K / kGroup) * kBN * 2;
+    p.load_stages = (kMaxSmemBytes - fixed) / kLoadBytes;
+    if (p.load_stages > kMaxLoadStages) p.load_stages = kMaxLoadStages;
+    if (g_prefill_depth > 0 && g_prefill_depth < p.load_stages) p.load_stages = g_prefill_depth;
+    const int smem_bytes = fixed + p.load_stages * kLoadBytes;
     const int sms = num_sms();
     if (sms <= 0) return cudaErrorInvalidDevice;
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sms ? tiles : sms;
-    if (sub) w4a16_prefill_kernel<true><<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmW, p);
-    else w4a16_prefill_kernel<false><<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(tmX, tmW, p);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define B200Q_PREFILL(SUB_, TEAMS_, WIDE_)                                                                                  \
+    do {                                                                                                                   \
+        auto kern = w4a16_prefill_kernel<SUB_, TEAMS_, WIDE_>;                                                             \
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);            \
+        if (e != cudaSuccess) return e;                                                                                    \
+        kern<<<grid, kThreads + 32 * kConvWarps * (TEAMS_ - 1), smem_bytes, st>>>(tmX, tmW, p);                            \
+    } while (0)
+    const int v = g_prefill_variant;
+    if (sub) { if (v == 1) B200Q_PREFILL(true, 1, true); else if (v == 2) B200Q_PREFILL(true, 2, false); else B200Q_PREFILL(true, 1, false); }
+    else { if (v == 1) B200Q_PREFILL(false, 1, true); else if (v == 2) B200Q_PREFILL(false, 2, false); else B200Q_PREFILL(false, 1, false); }
+#undef B200Q_PREFILL
     return cudaGetLastError();
 }
 
