@@ -431,8 +431,9 @@ def multi_rank_parity(mlp, x, rank, world, dev):
     dist_ulp = ((yf - wf).abs() / ulp)[big].max()
     out = {"replicas_equal": bool(eq.item()), "exact_frac": float((y == want).float().mean().item()),
            "max_ulp_vs_rank_order_sum": float(dist_ulp.item()),
-           "transport": ("multimem (in-switch reduction)" if getattr(mlp, "multicast", False) else "peer loads/stores") +
-                        (", result gathered by copy engines" if mlp.comm == "pipelined_ce" else ""),
+           "transport": ("copy engines both ways, local sum kernel" if mlp.comm == "pipelined_copy" else
+                         ("multimem (in-switch reduction)" if getattr(mlp, "multicast", False) else "peer loads/stores") +
+                         (", result gathered by copy engines" if mlp.comm == "pipelined_ce" else "")),
            "comm": mlp.comm}
     if rank == 0:
         g = torch.Generator().manual_seed(11)
@@ -649,7 +650,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--chunks", type=int, default=4, help="token chunks for all-reduce overlap (N > 1)")
-    ap.add_argument("--comm", default="pipelined", choices=["auto", "pipelined", "pipelined_ce", "fused", "symm", "nccl"],
+    ap.add_argument("--comm", default="pipelined", choices=["auto", "pipelined", "pipelined_ce", "pipelined_copy", "fused", "symm", "nccl"],
                     help="all-reduce: the library's NVSwitch kernel over symmetric memory, or NCCL")
     ap.add_argument("--ar-ctas", type=int, default=None, help="CTAs of the stand-alone all-reduce kernel (default: by transport)")
     ap.add_argument("--partial", default="bf16", choices=["bf16", "fp32"], help="dtype of the partial outputs that cross NVLink")

@@ -80,6 +80,7 @@ _SIGNATURES = {
     "b200q_fp8_set_sm_limit": [_I],
     "b200q_allreduce_set_reserved_smem": [_I],
     "b200q_fp8_set_reducer_stride": [_I],
+    "b200q_sum_to_bf16": [_VP, _I, _I, _VP, C.c_longlong, _I, _VP],
     "b200q_reduce_scatter_to_bf16": [_VP, _VP, _VP, _VP, _I, C.c_longlong, C.c_longlong, _I, _I, C.c_uint, C.c_uint, _I, _VP],
     "b200q_allreduce_to_bf16": [_VP, _VP, _VP, _VP, _VP, _I, C.c_longlong, C.c_longlong, _I, _I, C.c_uint, C.c_uint, _I, _VP],
     "b200q_allreduce_set_unroll": [_I],

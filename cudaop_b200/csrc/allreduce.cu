@@ -116,6 +116,27 @@ allreduce_one_device_kernel(Params p, int ctas_per_rank)
     allreduce_body<false, PartialBf16, 2, SCATTER>(p, blockIdx.x % ctas_per_rank, ctas_per_rank);
 }
 
+// out[e] = bf16( sum over i of src_i[e] ), fp32 accumulation in index order, one rounding: the arithmetic of the
+// exchange on buffers that all live in this device's memory (the sources were brought here by copy engines).
+template <bool PartialBf16>
+__global__ void __launch_bounds__(256) sum_to_bf16_kernel(const void* const* srcs, int n, __nv_bfloat16* out, long long elems)
+{
+    constexpr int U = 4;
+    const long long vecs = elems / 8;
+    const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+    for (long long vb = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; vb < vecs; vb += stride * U) {
+        uint4 o[U];
+        long long e[U];
+        bool valid[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) { valid[u] = vb + u * stride < vecs; e[u] = (vb + u * stride) * 8; }
+        arc::reduce8xU<false, PartialBf16, U>(srcs, nullptr, n, e, valid, o);
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (valid[u]) *reinterpret_cast<uint4*>(out + e[u]) = o[u];
+    }
+}
+
 // One tiny CTA: a barrier over all ranks on the launching streams (bounded like every other wait).
 __global__ void __launch_bounds__(32) rank_barrier_kernel(const Params p)
 {
@@ -250,6 +271,18 @@ int b200q_reduce_scatter_to_bf16_one_device(const void* const* partial_ptrs_dev,
 {
     return one_device(partial_ptrs_dev, out_ptrs_dev, signal_ptrs_dev, partial_is_bf16, elem_offset, elems, world, epoch,
                       signal_offset_bytes, ctas_per_rank, true, stream);
+}
+
+int b200q_sum_to_bf16(const void* const* srcs_dev, int n, int src_is_bf16, void* out, long long elems, int ctas, void* stream)
+{
+    using namespace b200q;
+    if (srcs_dev == nullptr || out == nullptr || n < 1 || n > ar::kMaxWorld || elems <= 0 || elems % 8 != 0 || !aligned16(out))
+        return cudaErrorInvalidValue;
+    if (ctas < 1 || ctas > 1024) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (src_is_bf16) ar::sum_to_bf16_kernel<true><<<ctas, 256, 0, s>>>(srcs_dev, n, static_cast<__nv_bfloat16*>(out), elems);
+    else ar::sum_to_bf16_kernel<false><<<ctas, 256, 0, s>>>(srcs_dev, n, static_cast<__nv_bfloat16*>(out), elems);
+    return cudaGetLastError();
 }
 
 size_t b200q_rank_barrier_signal_bytes(void) { return static_cast<size_t>(b200q::ar::kMaxWorld) * sizeof(uint32_t); }

@@ -103,18 +103,19 @@ class TensorParallelMLP:
         self._epoch = 0
         if world > 1:
             self.comm = comm
-            if comm in ("auto", "fused", "symm", "pipelined", "pipelined_ce"):
+            if comm in ("auto", "fused", "symm", "pipelined", "pipelined_ce", "pipelined_copy"):
                 try:
                     self._nbuf = 2 if comm.startswith("pipelined") else 1
+                    self._copy_mode = comm == "pipelined_copy"
                     self._init_symmetric(T, H)
-                    self.comm = comm if comm in ("symm", "pipelined", "pipelined_ce") else "fused"
+                    self.comm = comm if comm in ("symm", "pipelined", "pipelined_ce", "pipelined_copy") else "fused"
                 except Exception as exc:
                     if comm != "auto":
                         raise
                     warnings.warn(f"symmetric memory is not available ({type(exc).__name__}: {exc}); "
                                   "the all-reduce falls back to NCCL on fp32 partials")
                     self.comm = "nccl"
-            if self.comm in ("fused", "pipelined", "pipelined_ce"):
+            if self.comm in ("fused", "pipelined", "pipelined_ce", "pipelined_copy"):
                 self.chunks = 1
             self._buf = 0
             self._ar_done = [None, None]
@@ -153,12 +154,17 @@ class TensorParallelMLP:
         # every peer's output buffers as tensors this rank can copy from (copy-engine half of "pipelined_ce")
         self._y_peer = [self._hy.get_buffer(r, (nb, T, H), torch.bfloat16, 0) if r != self.rank else None
                         for r in range(self.world)]
+        self._p_peer = [self._hp.get_buffer(r, (nb, T, H), self.partial_dtype, 0) if r != self.rank else None
+                        for r in range(self.world)]
         self._ce_streams = [torch.cuda.Stream(device=dev) for _ in range(min(4, self.world - 1))]
         self._bar_epoch = 0
+        self._stage_buf = None        # "pipelined_copy": the peers' partial sums of this rank's part, brought here by copies
         # launch shape of the stand-alone all-reduce kernel, from measurements at 2/4/8 ranks: the
         # in-switch reduction saturates with few threads (and then disturbs a co-running GEMM least),
         # peer loads need many requests in flight from every SM
         L = ops.lib()
+        if getattr(self, "_copy_mode", False) and self.ar_ctas is None:
+            self.ar_ctas = 32                   # the local sum kernel: 64 MB of local reads at most
         if self.multicast:
             L.b200q_allreduce_set_threads(256); L.b200q_allreduce_set_unroll(4)
             if self.ar_ctas is None:
@@ -237,7 +243,7 @@ class TensorParallelMLP:
         T, H = x.shape
         if H != self.hidden or T > self.max_tokens:
             raise ValueError(f"x must be [<= {self.max_tokens}, {self.hidden}]")
-        if self.comm in ("pipelined", "pipelined_ce"):
+        if self.comm in ("pipelined", "pipelined_ce", "pipelined_copy"):
             return self._forward_pipelined(x, T)
         if self.comm in ("symm", "fused"):
             y = self.y_sym[:T]
@@ -293,6 +299,8 @@ class TensorParallelMLP:
                 self.comm_stream.wait_event(done)
                 if self.comm == "pipelined_ce":
                     launches += self._reduce_scatter_then_copies(T, b)
+                elif self.comm == "pipelined_copy":
+                    launches += self._exchange_by_copies(T, b)
                 else:
                     self._allreduce_chunk(0, T, buf=b)
                 ev = torch.cuda.Event(); ev.record(self.comm_stream)
@@ -300,6 +308,57 @@ class TensorParallelMLP:
             self.output_ready = ev
         self.kernel_launches_per_forward = launches + 1
         return self._y_all[b][:T]
+
+    def _barrier(self, stream):
+        self._bar_epoch += 1
+        ops._raise(ops.lib().b200q_rank_barrier(self._hf.buffer_ptrs_dev, self.rank, self.world, self._bar_epoch,
+                                                self._bar_offset, stream.cuda_stream), "b200q_rank_barrier")
+
+    def _pull(self, after, pairs):
+        """Device-to-device copies (dst, src) spread over the copy streams, all behind event `after`; the side
+        stream then waits for them."""
+        cs = self.comm_stream
+        for k, (dst, src) in enumerate(pairs):
+            st = self._ce_streams[k % len(self._ce_streams)]
+            st.wait_event(after)
+            with torch.cuda.stream(st):
+                dst.copy_(src, non_blocking=True)
+        for st in self._ce_streams:
+            cs.wait_stream(st)
+
+    def _exchange_by_copies(self, T, b):
+        """The whole exchange on copy engines: behind a barrier every rank copies the peers' partial sums of ITS 1/R of
+        the output into local staging, a small local kernel adds them in rank order (fp32, one rounding: bit for bit
+        the rank-order sum) into its own output buffer, and behind a second barrier the ranks copy each other's
+        parts.  No SM moves NVLink traffic; the only kernel beside the GEMMs reads local memory.  Staging is reused
+        every step: the copies of step i+1 are ordered behind the sum of step i on the side stream.  Returns the
+        number of kernel launches beyond the one the caller counts for the exchange."""
+        L = ops.lib(); H = self.hidden; R = self.world
+        n = T * H
+        if n % (8 * R) != 0:
+            raise ValueError("tokens * hidden must be divisible by 8 * world")
+        per = n // R
+        cs = self.comm_stream
+        if self._stage_buf is None or self._stage_buf.shape[1] < per:
+            self._stage_buf = torch.empty((R, self.max_tokens * H // R), dtype=self.partial_dtype, device=self.device)
+            self._src_tables = {}
+        lo, hi = self.rank * per, (self.rank + 1) * per
+        mine_p = self._partial_all[b].view(-1)
+        key = (b, per)
+        if key not in self._src_tables:        # rank order: the own partial in place, the others from staging
+            ptrs = [mine_p[lo:hi].data_ptr() if r == self.rank else self._stage_buf[r, :per].data_ptr() for r in range(R)]
+            self._src_tables[key] = torch.tensor(ptrs, dtype=torch.int64, device=self.device)
+        self._barrier(cs)                      # every rank's down projection of this step has finished
+        ready = torch.cuda.Event(); ready.record(cs)
+        order = [(self.rank + d) % R for d in range(1, R)]
+        self._pull(ready, [(self._stage_buf[r, :per], self._p_peer[r][b].view(-1)[lo:hi]) for r in order])
+        y = self._y_all[b].view(-1)
+        ops._raise(L.b200q_sum_to_bf16(self._src_tables[key].data_ptr(), R, int(self.partial_dtype == torch.bfloat16),
+                                       y[lo:hi].data_ptr(), per, self.ar_ctas, cs.cuda_stream), "b200q_sum_to_bf16")
+        self._barrier(cs)                      # every rank's part of the result is complete
+        summed = torch.cuda.Event(); summed.record(cs)
+        self._pull(summed, [(y[r * per:(r + 1) * per], self._y_peer[r][b].view(-1)[r * per:(r + 1) * per]) for r in order])
+        return 2                               # two barriers and the sum; the caller counts one exchange kernel itself
 
     def _reduce_scatter_then_copies(self, T, b):
         """The exchange in two phases on the side stream: a kernel sums this rank's 1/R of the output into its own

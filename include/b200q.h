@@ -202,6 +202,11 @@ int b200q_reduce_scatter_to_bf16(const void* const* partial_ptrs_dev, void* cons
                                  void* const* signal_ptrs_dev, const void* partial_multicast, int partial_is_bf16,
                                  long long elem_offset, long long elems, int rank, int world, unsigned int epoch,
                                  unsigned int signal_offset_bytes, int ctas, void* stream);
+/* out[e] = bf16( sum_i src_i[e] ) for `n` arrays of this device (fp32 or bf16), fp32 accumulation in index order,
+ * one round-to-nearest-even: the arithmetic of the exchange alone, for callers that move the ranks' partial sums
+ * with copy engines (device-to-device copies behind b200q_rank_barrier) so that no SM is busy with NVLink traffic
+ * beside a running GEMM.  `srcs_dev`: device array of n pointers, 16-byte aligned; elems % 8 == 0. */
+int b200q_sum_to_bf16(const void* const* srcs_dev, int n, int src_is_bf16, void* out, long long elems, int ctas, void* stream);
 int b200q_allreduce_set_unroll(int unroll);     /* tuning knob: independent reductions in flight per thread, 1..8 */
 int b200q_allreduce_set_threads(int threads);   /* tuning knob: threads per CTA of the all-reduce kernel, 128/256/512 */
 size_t b200q_allreduce_signal_bytes(void);

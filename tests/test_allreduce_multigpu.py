@@ -29,7 +29,7 @@ def _worker(rank, world, port, mode, pdt, out_dir):
     ts = [torch.from_numpy(np.ascontiguousarray(t)) for t in case[1:]]
     comm = {"multicast": "symm", "p2p": "symm", "nccl": "nccl", "fused": "fused", "fused_p2p": "fused",
             "pipelined": "pipelined", "pipelined_mc": "pipelined",
-            "pipelined_ce": "pipelined_ce", "pipelined_ce_mc": "pipelined_ce"}[mode]
+            "pipelined_ce": "pipelined_ce", "pipelined_ce_mc": "pipelined_ce", "pipelined_copy": "pipelined_copy"}[mode]
     pdtype = torch.bfloat16 if pdt == "bf16" else torch.float32
     mlp = TensorParallelMLP(*ts, rank=rank, world=world, max_tokens=T, chunks=2, comm=comm, partial_dtype=pdtype,
                             use_multicast=mode in ("multicast", "fused", "pipelined_mc", "pipelined_ce_mc"))
@@ -58,13 +58,13 @@ def _worker(rank, world, port, mode, pdt, out_dir):
     dist.barrier(); dist.destroy_process_group()
 
 
-MODES = ["pipelined", "pipelined_mc", "fused", "fused_p2p", "multicast", "p2p", "nccl", "pipelined_ce", "pipelined_ce_mc"]
+MODES = ["pipelined", "pipelined_mc", "fused", "fused_p2p", "multicast", "p2p", "nccl", "pipelined_ce", "pipelined_ce_mc", "pipelined_copy"]
 
 
 # two ranks: every transport and both partial types; four and eight ranks: the modes the benchmark times
 # (side-stream all-reduce through the switch / by peer loads, and the fused latency mode) on bf16 partials
 CASES = [(2, m, d) for m in MODES for d in ("bf16", "fp32")] + \
-        [(w, m, "bf16") for w in (4, 8) for m in ("pipelined_mc", "pipelined", "fused", "pipelined_ce_mc", "pipelined_ce")]
+        [(w, m, "bf16") for w in (4, 8) for m in ("pipelined_mc", "pipelined", "fused", "pipelined_ce_mc", "pipelined_ce", "pipelined_copy")]
 
 
 @pytest.mark.parametrize("world,mode,pdt", CASES)

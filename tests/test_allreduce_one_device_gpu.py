@@ -86,6 +86,26 @@ def test_reduce_scatter_kernel_all_ranks_in_one_launch(world, pdt):
             assert bool((rest == -7.0).all())
 
 
+@pytest.mark.parametrize("pdt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n", [1, 2, 8])
+def test_local_sum_kernel(n, pdt):
+    """b200q_sum_to_bf16: fp32 sum in index order of n local arrays, one rounding (the arithmetic of the exchange
+    when copy engines move the data)."""
+    import cudaop_b200 as ops
+    L = ops.lib()
+    g = torch.Generator(device="cuda").manual_seed(300 + n)
+    elems = 8 * 12347
+    parts = [torch.randn(elems, device="cuda", generator=g).to(pdt) for _ in range(n)]
+    out = torch.zeros(elems, dtype=torch.bfloat16, device="cuda")
+    tp = _ptr_table(parts)
+    rc = L.b200q_sum_to_bf16(tp.data_ptr(), n, int(pdt == torch.bfloat16), out.data_ptr(), elems, 7,
+                             torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out, _rank_order_sum(parts))
+    assert L.b200q_sum_to_bf16(tp.data_ptr(), n, 1, out.data_ptr(), elems + 4, 7, None) == 1      # refused: elems % 8
+
+
 def test_reduce_scatter_one_rank_world():
     """world = 1 through the per-rank entry point: the rank's own partial, rounded once."""
     import cudaop_b200 as ops
