@@ -57,6 +57,24 @@ def shard_mlp_weights(w_gate, s_gate, w_up, s_up, w_down, s_down, rank: int, wor
             w_down[:, lo:hi].contiguous(), s_down.contiguous())
 
 
+def copy_exchange_plan(rank: int, world: int, elems: int):
+    """The copy-engine exchange of `elems` output elements as plain index ranges (no device needed).
+
+    Returns ``(mine, pulls_partial, pulls_result)``: rank r owns ``mine = (r*n/R, (r+1)*n/R)``; first it copies
+    that range of every peer's partial sums to itself (``pulls_partial``: peers in the order r+1, r+2, ... so that at
+    any moment the ranks read from different peers), adds the R contributions in rank order, and then copies
+    every peer's own range of the result (``pulls_result``: ``(peer, lo, hi)``).  Mirrors the two phases of the
+    ncclAllReduce in op/nccl/nccl_mlp_test.cu:181-195 (reduce-scatter, all-gather)."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("rank/world out of range")
+    if elems % (8 * world) != 0:
+        raise ValueError("the element count must be divisible by 8 * world")
+    per = elems // world
+    order = [(rank + d) % world for d in range(1, world)]
+    mine = (rank * per, (rank + 1) * per)
+    return mine, [(r, mine[0], mine[1]) for r in order], [(r, r * per, (r + 1) * per) for r in order]
+
+
 class TensorParallelMLP:
     """Y = down( silu(X Wg^T) * (X Wu^T) ), weights E4M3 with per-output-channel scales."""
 
@@ -335,14 +353,12 @@ class TensorParallelMLP:
         number of kernel launches beyond the one the caller counts for the exchange."""
         L = ops.lib(); H = self.hidden; R = self.world
         n = T * H
-        if n % (8 * R) != 0:
-            raise ValueError("tokens * hidden must be divisible by 8 * world")
-        per = n // R
+        (lo, hi), pulls_partial, pulls_result = copy_exchange_plan(self.rank, R, n)
+        per = hi - lo
         cs = self.comm_stream
         if self._stage_buf is None or self._stage_buf.shape[1] < per:
             self._stage_buf = torch.empty((R, self.max_tokens * H // R), dtype=self.partial_dtype, device=self.device)
             self._src_tables = {}
-        lo, hi = self.rank * per, (self.rank + 1) * per
         mine_p = self._partial_all[b].view(-1)
         key = (b, per)
         if key not in self._src_tables:        # rank order: the own partial in place, the others from staging
@@ -350,14 +366,13 @@ class TensorParallelMLP:
             self._src_tables[key] = torch.tensor(ptrs, dtype=torch.int64, device=self.device)
         self._barrier(cs)                      # every rank's down projection of this step has finished
         ready = torch.cuda.Event(); ready.record(cs)
-        order = [(self.rank + d) % R for d in range(1, R)]
-        self._pull(ready, [(self._stage_buf[r, :per], self._p_peer[r][b].view(-1)[lo:hi]) for r in order])
+        self._pull(ready, [(self._stage_buf[r, :per], self._p_peer[r][b].view(-1)[a:z]) for r, a, z in pulls_partial])
         y = self._y_all[b].view(-1)
         ops._raise(L.b200q_sum_to_bf16(self._src_tables[key].data_ptr(), R, int(self.partial_dtype == torch.bfloat16),
                                        y[lo:hi].data_ptr(), per, self.ar_ctas, cs.cuda_stream), "b200q_sum_to_bf16")
         self._barrier(cs)                      # every rank's part of the result is complete
         summed = torch.cuda.Event(); summed.record(cs)
-        self._pull(summed, [(y[r * per:(r + 1) * per], self._y_peer[r][b].view(-1)[r * per:(r + 1) * per]) for r in order])
+        self._pull(summed, [(y[a:z], self._y_peer[r][b].view(-1)[a:z]) for r, a, z in pulls_result])
         return 2                               # two barriers and the sum; the caller counts one exchange kernel itself
 
     def _reduce_scatter_then_copies(self, T, b):

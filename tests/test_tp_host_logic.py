@@ -9,7 +9,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 import oracle
-from cudaop_b200.mlp import shard_mlp_weights
+from cudaop_b200.mlp import copy_exchange_plan, shard_mlp_weights
 
 
 def test_shard_rule_matches_the_reference_layouts():
@@ -75,3 +75,39 @@ def test_two_gloo_ranks_reduce_to_identical_replicas(tmp_path):
     y_full = oracle.gemm_f32(oracle.decode_e4m3(hq), oracle.decode_e4m3(wd)) * (sh[:, None] * sd[None, :])
     rel = np.linalg.norm(r0["y"].float().numpy() - y_full) / np.linalg.norm(y_full)
     assert rel < 3e-2, rel
+
+
+def test_copy_exchange_plan_reproduces_the_rank_order_sum_on_every_rank():
+    """The index plan of the copy-engine exchange, played on the host for 1, 2, 4 and 8 ranks: every rank ends
+    with the fp32 rank-order sum rounded once, and at every step of the first phase the ranks read from
+    pairwise different peers."""
+    import pytest
+    rng = np.random.default_rng(3)
+    for world in (1, 2, 4, 8):
+        n = 8 * world * 5
+        partial = [torch.from_numpy(rng.standard_normal(n).astype(np.float32)).to(torch.bfloat16) for _ in range(world)]
+        want = torch.zeros(n)
+        for p in partial:
+            want += p.float()
+        want = want.to(torch.bfloat16)
+        plans = [copy_exchange_plan(r, world, n) for r in range(world)]
+        y = [torch.full((n,), float("nan"), dtype=torch.bfloat16) for _ in range(world)]
+        for r, ((lo, hi), pulls, _) in enumerate(plans):
+            staged = {peer: partial[peer][a:z].clone() for peer, a, z in pulls}
+            assert all((a, z) == (lo, hi) for _, a, z in pulls) and sorted(staged) == [q for q in range(world) if q != r]
+            acc = torch.zeros(hi - lo)
+            for q in range(world):                        # rank order, the own part read in place
+                acc += (partial[r][lo:hi] if q == r else staged[q]).float()
+            y[r][lo:hi] = acc.to(torch.bfloat16)
+        for r, (_, _, pulls) in enumerate(plans):
+            for peer, a, z in pulls:
+                assert (a, z) == plans[peer][0]           # a peer's own range, which that peer has summed
+                y[r][a:z] = y[peer][a:z]
+        for r in range(world):
+            assert torch.equal(y[r], want)
+        for step in range(world - 1):                     # no two ranks pull from the same peer at the same step
+            assert len({plans[r][1][step][0] for r in range(world)}) == world
+    with pytest.raises(ValueError):
+        copy_exchange_plan(0, 3, 100)
+    with pytest.raises(ValueError):
+        copy_exchange_plan(2, 2, 32)
