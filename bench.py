@@ -534,7 +534,12 @@ def run_ours(args):
         sampler.start()
     # ---- device-resident steps (the headline `value`) with events around the top kernel
     mlp.top_kernel_events = []
-    ms_step = timed(lambda: mlp.forward(x), args.steps, args.warmup, finish=mlp.wait)
+    def device_step():
+        mlp.forward(x)
+        if not args.no_prepare:       # the next (independent) batch is quantised beside this batch's GEMMs
+            mlp.prepare(x)
+    ms_step = timed(device_step, args.steps, args.warmup, finish=mlp.wait)
+    mlp.cancel_prepared()
     evs = mlp.top_kernel_events; mlp.top_kernel_events = None
     torch.cuda.synchronize()
     top_ms = [a.elapsed_time(b) for a, b in evs[-args.steps * max(1, mlp.chunks if world > 1 else 1):]]
@@ -560,7 +565,7 @@ def run_ours(args):
     # PCIe link, the ranks complete each other's X over NVLink (copy engines, ordered by a stream barrier), and each
     # rank writes back 1/R of the replicated result.  Copies are double-buffered on their own streams.
     from cudaop_b200.mlp import HostFedMLP
-    fed = HostFedMLP(mlp, TOKENS)
+    fed = HostFedMLP(mlp, TOKENS, prepare_ahead=not args.no_prepare)
 
     def e2e_step():
         fed.step(x_host, y_host)
@@ -600,9 +605,12 @@ def run_ours(args):
                         "1/R of X in and 1/R of Y out over its own PCIe link and pulls the rest of X from its peers "
                         "over NVLink (copy engines) behind a stream-ordered rank barrier"},
         "latency_ms_per_forward": ms_latency,
-        "overlap": ("steps are independent batches: the all-reduce of step i runs on a side stream under the GEMMs "
-                    "of step i+1 (double-buffered); latency_ms_per_forward is one forward alone with the all-reduce "
-                    "fused into the down-projection kernel") if world > 1 and mlp.comm.startswith("pipelined") else "none",
+        "overlap": (("steps are independent batches: the all-reduce of step i runs on a side stream under the GEMMs "
+                     "of step i+1 (double-buffered); latency_ms_per_forward is one forward alone with the all-reduce "
+                     "fused into the down-projection kernel; ") if world > 1 and mlp.comm.startswith("pipelined") else "") +
+                   ("the activation quantiser of batch i+1 runs on a side stream beside the GEMMs of batch i "
+                    "(TensorParallelMLP.prepare); every step still launches it once" if not args.no_prepare else
+                    "none between batches"),
         "gpu_launches": launches, "kernels_ms": kernels_ms,
         "roofline": {"bound": "tensor", "kernel": "gemm_fp8_2cta_kernel<SwiGLU> (gate/up projection, CTA pairs)",
                      "achieved": top_tf, "peak": peak_burst, "unit": "TFLOP/s", "frac": top_tf / peak_burst,
@@ -658,6 +666,8 @@ def main():
                     help="reduce and broadcast in the NVSwitch (multimem) instead of peer loads/stores; auto = from 4 ranks on")
     ap.add_argument("--cpu-tokens", type=int, default=64, help="tokens in the CPU-baseline sample")
     ap.add_argument("--cpu-tokens-single", type=int, default=4, help="tokens in the single-thread CPU sample")
+    ap.add_argument("--no-prepare", action="store_true",
+                    help="quantise each batch inside its own forward instead of beside the previous batch's GEMMs")
     ap.add_argument("--static-tiles", action="store_true",
                     help="CTA-pair FP8 kernels with fixed round-robin tile shares instead of the global tile counter")
     ap.add_argument("--no-cases", action="store_true")

@@ -98,6 +98,12 @@ class TensorParallelMLP:
         # workspaces: allocated once, reused by every forward
         self.xq = torch.empty((T, H), dtype=torch.uint8, device=dev)
         self.sx = torch.empty((T,), dtype=torch.float32, device=dev)
+        # prepare(): the next batch's activations are quantised on a side stream while this batch's GEMMs run
+        self._prep_stream = None
+        self._prep = None             # (data_ptr, tokens, slot) of the batch prepare() has quantised
+        self._prep_slot = 0
+        self._prep_xq, self._prep_sx = [None, None], [None, None]
+        self._prep_ready, self._prep_free = [None, None], [None, None]
         self.h = torch.empty((T, Il), dtype=torch.bfloat16, device=dev)
         self.hq = torch.empty((T, Il), dtype=torch.uint8, device=dev)
         self.shs = torch.empty((T,), dtype=torch.float32, device=dev)
@@ -213,13 +219,18 @@ class TensorParallelMLP:
         n = hi - lo
         H, Il = self.hidden, self.inter_local
         xq, sx, h, hq, shs = self.xq[lo:hi], self.sx[lo:hi], self.h[lo:hi], self.hq[lo:hi], self.shs[lo:hi]
+        pre = self._take_prepared(x, lo, hi)
         marks = [] if self.stage_events is not None else None
 
         def mark():
             if marks is not None:
                 e = torch.cuda.Event(enable_timing=True); e.record(); marks.append(e)
         mark()
-        ops._raise(L.b200q_quant_rows_e4m3(x[lo:hi].data_ptr(), xq.data_ptr(), sx.data_ptr(), n, H, st), "quant x")
+        if pre is None:
+            ops._raise(L.b200q_quant_rows_e4m3(x[lo:hi].data_ptr(), xq.data_ptr(), sx.data_ptr(), n, H, st), "quant x")
+        else:                         # quantised ahead of time by prepare(): wait for that kernel, read its buffers
+            torch.cuda.current_stream().wait_event(self._prep_ready[pre])
+            xq, sx = self._prep_xq[pre][:n], self._prep_sx[pre][:n]
         mark()
         ev = self.top_kernel_events
         if ev is not None:
@@ -230,6 +241,9 @@ class TensorParallelMLP:
         if ev is not None:
             e1 = torch.cuda.Event(enable_timing=True); e1.record()
             ev.append((e0, e1))
+        if pre is not None:           # the slot may be overwritten once this GEMM has read it
+            free = torch.cuda.Event(); free.record()
+            self._prep_free[pre] = free
         mark()
         ops._raise(L.b200q_quant_rows_e4m3(h.data_ptr(), hq.data_ptr(), shs.data_ptr(), n, Il, st), "quant h")
         mark()
@@ -255,6 +269,49 @@ class TensorParallelMLP:
         if marks is not None:
             self.stage_events.append(marks)
         return 4
+
+    def prepare(self, x: torch.Tensor, ready: "torch.cuda.Event | None" = None):
+        """Quantises the NEXT batch's activations now, on a side stream, so that the kernel runs beside the GEMMs
+        already enqueued instead of in front of the next forward().  `x` must be complete when `ready` fires (None:
+        it already is — the side stream does not wait for the current stream) and must not change until the
+        forward(x) that consumes it has been issued; that forward recognises the batch by its address and size.
+        Independent batches only: the reference's benchmark loop (op/nccl/nccl_mlp_test.cu:483-526) is of that kind."""
+        ops._check(x, "x", (torch.bfloat16,), 2)
+        T, H = x.shape
+        if H != self.hidden or T > self.max_tokens:
+            raise ValueError(f"x must be [<= {self.max_tokens}, {self.hidden}]")
+        with torch.cuda.device(self.device):
+            if self._prep_stream is None:
+                self._prep_stream = torch.cuda.Stream(device=self.device)
+                for i in range(2):
+                    self._prep_xq[i] = torch.empty((self.max_tokens, H), dtype=torch.uint8, device=self.device)
+                    self._prep_sx[i] = torch.empty((self.max_tokens,), dtype=torch.float32, device=self.device)
+            slot = self._prep_slot
+            self._prep_slot ^= 1
+            ps = self._prep_stream
+            if ready is not None:
+                ps.wait_event(ready)
+            if self._prep_free[slot] is not None:
+                ps.wait_event(self._prep_free[slot])
+            ops._raise(ops.lib().b200q_quant_rows_e4m3(x.data_ptr(), self._prep_xq[slot].data_ptr(), self._prep_sx[slot].data_ptr(),
+                                                       T, H, ps.cuda_stream), "quant x (prepare)")
+            ev = torch.cuda.Event(); ev.record(ps)
+            self._prep_ready[slot] = ev
+            self._prep = (x.data_ptr(), T, slot)
+
+    def cancel_prepared(self):
+        """Forgets a batch that prepare() quantised and no forward() has consumed."""
+        self._prep = None
+
+    def _take_prepared(self, x, lo, hi):
+        """The slot prepare() filled for exactly this batch (whole token range), or None."""
+        if self._prep is None:
+            return None
+        ptr, T, slot = self._prep
+        if ptr != x.data_ptr() or lo != 0 or hi != T or x.shape[0] != T:
+            return None
+        self._prep = None
+        return slot
 
     def forward(self, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
         ops._check(x, "x", (torch.bfloat16,), 2)
@@ -441,8 +498,9 @@ class HostFedMLP:
     overwrites a slice only after every peer has read it.
     """
 
-    def __init__(self, mlp: TensorParallelMLP, tokens: int):
+    def __init__(self, mlp: TensorParallelMLP, tokens: int, prepare_ahead: bool = True):
         self.mlp, self.tokens = mlp, tokens
+        self.prepare_ahead = prepare_ahead
         self.rank, self.world, dev = mlp.rank, mlp.world, mlp.device
         H = mlp.hidden
         if tokens % self.world != 0 or tokens > mlp.max_tokens:
@@ -492,6 +550,8 @@ class HostFedMLP:
                         self.xbuf[b][r * rows:(r + 1) * rows].copy_(self._peer[r][b, r * rows:(r + 1) * rows], non_blocking=True)
             ready = torch.cuda.Event(); ready.record(self.copy_in)
         main.wait_event(ready)
+        if self.prepare_ahead:                         # quantise X beside the previous step's GEMMs
+            mlp.prepare(self.xbuf[b][:self.tokens], ready=ready)
         y = mlp.forward(self.xbuf[b][:self.tokens])
         done = torch.cuda.Event(); done.record(main)
         self._x_free[b] = done

@@ -104,3 +104,29 @@ def test_two_rank_shards_sum_to_the_single_rank_result(pdt):
         # fp32 partials (the reference's ncclFloat contract): the reduced output meets the bar
         # against the oracle's sum; bf16 partials are a stage of their own, checked above
         assert_bar(y2.cpu().numpy(), ref_sum, I, "tp2 sum")
+
+
+def test_prepare_quantises_the_next_batch_ahead_with_the_same_bits():
+    """prepare(x) on the side stream, then forward(x): identical output to a forward that quantises by itself;
+    the two slots alternate; a forward on a DIFFERENT tensor ignores the prepared batch."""
+    from cudaop_b200.mlp import TensorParallelMLP
+    import cudaop_b200 as ops
+    T, H, I = 192, 512, 1024
+    case = oracle.make_mlp_case(T, H, I, seed=13)
+    mlp = TensorParallelMLP(*_tensors(case), max_tokens=T)
+    x = dev(case[0], torch.bfloat16)
+    y_plain = mlp(x).clone()
+    for _ in range(5):                                  # more steps than slots
+        mlp.prepare(x)
+        y = mlp(x)
+        assert mlp._prep is None                        # consumed
+        torch.cuda.synchronize()
+        assert torch.equal(y, y_plain)
+    x2 = (x.float() * 0.5).to(torch.bfloat16)
+    y2_plain = mlp(x2).clone()
+    mlp.prepare(x)
+    y2 = mlp(x2)                                        # another batch: quantised inside the forward
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y2_plain) and mlp._prep is not None
+    mlp.cancel_prepared()
+    assert mlp._prep is None and ops.status() == 0
