@@ -362,11 +362,13 @@ int gemm_w4a16_gemv(const void* X, const void* Wq, const void* S, void* Y, int M
 int gemm_w4a16_stream(const void* X, const void* Wq, const void* S, void* Y, int N, int K, int group, int pdl, void* stream);
 // gemm_w4a16_prefill.cu: many tokens, tcgen05 with group-wise partial-sum scaling (K % 128 == 0, K <= 16384)
 int gemm_w4a16_prefill(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, int sub, void* stream);
+// gemm_w4a16_prefill_ts.cu: many tokens, the converted weights as the tensor-memory operand (K % 128 == 0)
+int gemm_w4a16_prefill_ts(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, void* stream);
 }
 
 extern "C" int b200q_w4a16_set_impl(int impl)
 {
-    if (impl < 0 || impl > 7) return cudaErrorInvalidValue;
+    if (impl < 0 || impl > 8) return cudaErrorInvalidValue;
     b200q::w4tc::g_impl = impl;
     return 0;
 }
@@ -381,6 +383,8 @@ extern "C" int b200q_gemm_w4a16(const void* X, const void* Wq, const void* S, vo
                                 void* stream)
 {
     using namespace b200q;
+    if (w4tc::g_impl == 8 && group == 128 && K > 0 && K % 128 == 0)
+        return gemm_w4a16_prefill_ts(X, Wq, S, Y, M, N, K, group, stream);
     if (((M > 16 && w4tc::g_impl == 0) || w4tc::g_impl == 6 || w4tc::g_impl == 7) && group == 128 && K > 0 && K % 128 == 0 && K <= 16384)
         return gemm_w4a16_prefill(X, Wq, S, Y, M, N, K, group, w4tc::g_impl == 7 ? 1 : 0, stream);
     if (M == 1 && (w4tc::g_impl == 0 || w4tc::g_impl == 5) && group == 128 && K > 0 && K % 2048 == 0 && K <= 16384)

@@ -157,7 +157,8 @@ int b200q_w4a16_set_impl(int impl);     /* 0 = by M (default): streaming CUDA-co
                                          * a multiple of 2048 or exceeds 16384), warp-MMA kernel for 2..16 tokens, tcgen05
                                          * prefill kernel (group-wise partial-sum scaling) above 16; 5 / 6 = the streaming
                                          * GEMV / the prefill kernel wherever they apply; 7 = the prefill kernel whose
-                                         * converters subtract the integer offset themselves;
+                                         * converters subtract the integer offset themselves; 8 = the prefill kernel that
+                                         * keeps the converted weights in tensor memory (product computed transposed);
                                          * 1 = tcgen05 kernel; 2 = warp-MMA kernel for every M; 3 / 4 = the two GEMV forms
                                          * (shared memory + dp4a / registers + fp32) for up to 4 tokens */
 int b200q_w4a16_set_pdl(int on);        /* programmatic dependent launch of the GEMV / tcgen05 W4A16 kernels (default off):

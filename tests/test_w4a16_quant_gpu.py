@@ -100,11 +100,12 @@ def test_one_token_streaming_form_propagates_non_finite_activations(impl):
 
 @pytest.mark.parametrize("shape", [(17, 128, 128), (64, 256, 256), (200, 130, 1152), (129, 1000, 384), (512, 4096, 4096),
                                    (300, 72, 16384), (2, 40, 256)])
-@pytest.mark.parametrize("form", [6, 7])
+@pytest.mark.parametrize("form", [6, 7, 8])
 def test_prefill_form(shape, form, impl):
     """The tcgen05 prefill kernel (integer weights on the tensor core, the group's scale applied to its fp32 partial
-    sum), in both of its forms (6: the converters leave the offset 136 in and sixteen rows of ones take it out; 7: the
-    converters subtract it): ragged token and row counts, one to 128 groups; every output against the oracle."""
+    sum), in its forms (6: the converters leave the offset 136 in and sixteen rows of ones take it out; 7: the
+    converters subtract it; 8: the converted weights are the tensor-memory operand and the product is computed
+    transposed): ragged token and row counts, one to 128 groups; every output against the oracle."""
     import cudaop_b200 as ops
     if impl != (0, 0):
         pytest.skip("selects its own implementation")
