@@ -153,9 +153,9 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
             const int m0 = (tile / p.tiles_n) * kTok, n0 = (tile % p.tiles_n) * kRows;
             const int n = n0 + row;
             const __half* srow = p.S + static_cast<size_t>(n < p.N ? n : 0) * G;
-            float acc[64];
+            float2 acc[32];                                       // 64 tokens, two per packed fp32 operation
 #pragma unroll
-            for (int i = 0; i < 64; ++i) acc[i] = 0.0f;
+            for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.0f, 0.0f);
             float s_next = (n < p.N) ? __half2float(__ldg(srow)) : 0.0f;
             for (int g = 0; g < G && ok; ++g, ++gi) {
                 const float s = s_next;
@@ -170,7 +170,9 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
                     ptx::tmem_ld_32x32b_x16(taddr + 16 * c, d);
                     ptx::tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) acc[16 * c + i] = fmaf(__uint_as_float(d[i]), s, acc[16 * c + i]);
+                    for (int i = 0; i < 8; ++i)                    // fma.rn.f32x2: the same roundings as two scalar FMAs
+                        acc[8 * c + i] = __ffma2_rn(make_float2(__uint_as_float(d[2 * i]), __uint_as_float(d[2 * i + 1])),
+                                                    make_float2(s, s), acc[8 * c + i]);
                 }
                 ptx::tcgen05_fence_before_sync();
                 __syncwarp();
@@ -180,8 +182,10 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
             if (ok && n < p.N) {
                 __nv_bfloat16* dst = p.Y + static_cast<size_t>(m0 + 64 * half) * p.N + n;
 #pragma unroll
-                for (int j = 0; j < 64; ++j)
-                    if (m0 + 64 * half + j < p.M) dst[static_cast<size_t>(j) * p.N] = __float2bfloat16_rn(acc[j]);
+                for (int j = 0; j < 32; ++j) {
+                    if (m0 + 64 * half + 2 * j < p.M) dst[static_cast<size_t>(2 * j) * p.N] = __float2bfloat16_rn(acc[j].x);
+                    if (m0 + 64 * half + 2 * j + 1 < p.M) dst[static_cast<size_t>(2 * j + 1) * p.N] = __float2bfloat16_rn(acc[j].y);
+                }
             }
         }
     } else {
