@@ -60,24 +60,23 @@ struct Params {
     int M, N, K;
     int tiles_m, tiles_n;
     int load_stages;      // depth of the TMA ring: as deep as shared memory allows beside the scales of K / 128 groups
-    int dbg;
     uint32_t* status;
 };
 
 // SUB: the converters subtract the offset again (one exact bf16x2 subtraction per pair: 136 + q and q are both
 // bf16 integers), the B tile holds q itself, no rows of ones are multiplied and the fold is one fused
 // multiply-add per value.
-// TEAMS: teams of four converter warps; team t converts the stages whose running index is t modulo TEAMS.
-// WIDE: the fold reads 32 accumulator columns per tcgen05.ld (two round trips per group instead of four).
-// dbg (measurement only): bit 0 = converters write nothing, bit 1 = the fold adds nothing.
-template <bool SUB, int TEAMS, bool WIDE>
-__global__ void __launch_bounds__(kThreads + 32 * kConvWarps * (TEAMS - 1), 1)
+// Two teams of four converter warps: team t converts the stages whose running index is t modulo 2 (measured: +12 %
+// over one team; wider tcgen05.ld in the fold and a deeper load ring changed nothing).
+constexpr int kTeams = 2;
+template <bool SUB>
+__global__ void __launch_bounds__(kThreads + 32 * kConvWarps * (kTeams - 1), 1)
 w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-    constexpr int kWS = TEAMS > 1 ? 4 : 3;                  // converted tiles in flight
+    constexpr int kWS = 4;                  // converted tiles in flight
     const int LS = p.load_stages;
     const int G = p.K / kGroup;
     auto x_tile = [&](int s) { return smem_base + s * kXBytes; };
@@ -194,7 +193,7 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                 uint32_t ones[8] = {};
                 if (!SUB) ptx::tmem_ld_32x32b_x8(taddr + kBN, ones);   // sum over the group of this token's activations
                 float t = 0.0f;
-                constexpr int kCols = WIDE ? 32 : 16;                  // accumulator columns per tcgen05.ld
+                constexpr int kCols = 16;                              // accumulator columns per tcgen05.ld
 #pragma unroll
                 for (int c = 0; c < 64 / kCols; ++c) {                 // registers are the scarce resource
                     uint32_t d[kCols];
@@ -207,7 +206,6 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
                     }
                     ptx::tmem_ld_wait();
                     if (!SUB && c == 0) t = -136.0f * __uint_as_float(ones[0]);
-                    if (p.dbg & 2) continue;
 #pragma unroll
                     for (int i = 0; i < kCols / 2; ++i) {
                         const float2 sc2 = __half22float2(*reinterpret_cast<const __half2*>(&sw[i]));
@@ -260,14 +258,14 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         };
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             for (int i = 0; i < stages_per_tile; ++i, ++it) {
-                if (TEAMS > 1 && (it % TEAMS) != team) { advance(); continue; }
+                if ((it % kTeams) != team) { advance(); continue; }
                 if (!ptx::mbar_wait(full_bar(stage), phase, p.status, 36) ||
                     !ptx::mbar_wait(wfree_bar(wst), wphase ^ 1u, p.status, 37)) { ok = false; break; }
                 const uint4* wrow = reinterpret_cast<const uint4*>(smem_gen + (wp_tile(stage) - smem_base) + 32 * r);
                 const uint4 w0 = wrow[0], w1 = wrow[1];
                 const uint32_t ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-                for (int j = 0; j < ((p.dbg & 1) ? 0 : 8); ++j) {  // word j: K offsets 8 j .. 8 j + 7 of this stage
+                for (int j = 0; j < 8; ++j) {                      // word j: K offsets 8 j .. 8 j + 7 of this stage
                     // nibble pairs (i, i + 4) as bf16 integers 128 + (q + 8): (w & mask) ^ const does the sign flip and
                     // the exponent in one logic operation; then pairs of ascending K by byte permutes
                     uint32_t a0 = (ww[j] & 0x000F000Fu) ^ 0x43084308u;
@@ -300,13 +298,6 @@ w4a16_prefill_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 
 namespace b200q {
 
-int g_prefill_variant = 0, g_prefill_dbg = 0, g_prefill_depth = 0;
-extern "C" int b200q_w4a16_prefill_debug(int variant, int dbg, int depth)
-{
-    g_prefill_variant = variant; g_prefill_dbg = dbg; g_prefill_depth = depth;
-    return 0;
-}
-
 // Called by b200q_gemm_w4a16 for more than 16 tokens (K a multiple of 128, at most 16384).
 int gemm_w4a16_prefill(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, int sub, void* stream)
 {
@@ -329,29 +320,29 @@ int gemm_w4a16_prefill(const void* X, const void* Wq, const void* S, void* Y, in
             return cudaErrorInvalidValue;
     }
     if (!make_tmap_2d_u8(&tmW, Wq, N, K / 2, K / 2, kBN, kBK / 2, CU_TENSOR_MAP_SWIZZLE_NONE)) return cudaErrorInvalidValue;
-    p.dbg = g_prefill_dbg;
-    const int teams = g_prefill_variant == 2 ? 2 : 1;
-    const int fixed = 1024 + kBarBytes + (teams > 1 ? 4 : 3) * kWbBytes + (K / kGroup) * kBN * 2;
+    const int fixed = 1024 + kBarBytes + 4 * kWbBytes + (K / kGroup) * kBN * 2;
     p.load_stages = (kMaxSmemBytes - fixed) / kLoadBytes;
     if (p.load_stages > kMaxLoadStages) p.load_stages = kMaxLoadStages;
-    if (g_prefill_depth > 0 && g_prefill_depth < p.load_stages) p.load_stages = g_prefill_depth;
     const int smem_bytes = fixed + p.load_stages * kLoadBytes;
     const int sms = num_sms();
     if (sms <= 0) return cudaErrorInvalidDevice;
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sms ? tiles : sms;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define B200Q_PREFILL(SUB_, TEAMS_, WIDE_)                                                                                  \
-    do {                                                                                                                   \
-        auto kern = w4a16_prefill_kernel<SUB_, TEAMS_, WIDE_>;                                                             \
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);            \
-        if (e != cudaSuccess) return e;                                                                                    \
-        kern<<<grid, kThreads + 32 * kConvWarps * (TEAMS_ - 1), smem_bytes, st>>>(tmX, tmW, p);                            \
-    } while (0)
-    const int v = g_prefill_variant;
-    if (sub) { if (v == 1) B200Q_PREFILL(true, 1, true); else if (v == 2) B200Q_PREFILL(true, 2, false); else B200Q_PREFILL(true, 1, false); }
-    else { if (v == 1) B200Q_PREFILL(false, 1, true); else if (v == 2) B200Q_PREFILL(false, 2, false); else B200Q_PREFILL(false, 1, false); }
-#undef B200Q_PREFILL
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 64 && !configured[dev]) {
+        e = cudaFuncSetAttribute(w4a16_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(w4a16_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxSmemBytes);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    const int threads = kThreads + 32 * kConvWarps * (kTeams - 1);
+    if (sub) w4a16_prefill_kernel<true><<<grid, threads, smem_bytes, st>>>(tmX, tmW, p);
+    else w4a16_prefill_kernel<false><<<grid, threads, smem_bytes, st>>>(tmX, tmW, p);
     return cudaGetLastError();
 }
 

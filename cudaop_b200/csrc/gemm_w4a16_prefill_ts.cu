@@ -4,18 +4,28 @@
 // (op/test/arch_primitives/ptx_mma_integer.cu:93-108); S fp16, one per 128 K, no zero point.
 //
 // The product is computed transposed, D[n, m] = sum_k q[n,k] x[m,k], so that the operand that has to be
-// manufactured (integer weights as bf16) is the MMA's A operand and can live in tensor memory:
-//   warp 0       TMA producer: the 128-token x 64-K activation tile (128-byte swizzle) into a ring in shared memory
-//   warps 10..   converters, one thread per weight row and TMEM lane: 32 packed bytes per 64 K straight from
-//                global memory (requested two of the team's stages ahead), nibble pairs -> bf16 integers by one
-//                logic operation and one exact subtraction per pair, re-paired by byte permutes, one tcgen05.st of
-//                32 columns into a ring of eight A slots.  Teams of four warps take alternate stages.
-//   warp 1       MMA issuer: 4 x tcgen05.mma kind::f16 (A from tensor memory, 128 x 128 x 16) per stage, one 128-K
-//                scale group into one of two accumulators
+// manufactured (integer weights as bf16) is the MMA's A operand and can live in tensor memory.  One pipeline
+// step is one 128-K scale group:
+//   warp 0       TMA producer: the 128-token x 128-K activation tile (two 128-byte-swizzled boxes) into a ring in
+//                shared memory
+//   warps 10..   converters, one thread per weight row and TMEM lane: the row's 64 packed bytes of the group straight
+//                from global memory (requested one group ahead), nibble pairs -> bf16 integers by one
+//                logic operation and one exact subtraction per pair, re-paired by byte permutes, two tcgen05.st of 32
+//                columns into a ring of four A slots.
+//   warp 1       MMA issuer: 8 x tcgen05.mma kind::f16 (A from tensor memory, 128 x 128 x 16) into one of two
+//                accumulators, then ONE commit that tells the converters (A slot free) and the fold warps
+//                (accumulator complete), and one for the producer.
+// What sets the pace (timestamps written from inside the kernel, 4096^3): a group's eight MMAs take about 0.7 us
+// from commit to completion, 2.5 times their arithmetic: each 128 x 128 x 16 MMA adds to the accumulator the one
+// before it wrote, and 64 clocks of arithmetic do not cover that dependency.  Wider MMAs would, but two 256-column
+// accumulators and the weights do not fit the 512 columns of tensor memory together, and every group's accumulator
+// has to be read out for its scale.  A second team of converters, a second issuing thread, a deeper activation ring
+// and another tile order were measured and changed nothing beyond a few percent; 64-K steps were 25 % slower (the
+// issuing thread's chain of waits and commits per step).
 //   warps 2-9    fold: tcgen05.ld the group's accumulator and add s[n, g] * acc into fp32 registers -- the scale is
 //                one scalar per thread and group (lane = weight row); after the last group: bf16, stored transposed.
-// Against the form that converts through shared memory (gemm_w4a16_prefill.cu) a stage moves 32 KB less through
-// shared memory (no converted tile written and read back, no packed tile at all), which is what bounded that kernel.
+// Against the form that converts through shared memory (gemm_w4a16_prefill.cu) a group moves 80 KB less through
+// shared memory (no converted tile written and read back, no packed tile at all).
 // fp32 accumulation inside a group (tensor core) and across groups (registers); one rounding at the end; no product
 // q * s is ever rounded ("group-wise partial-sum scaling").
 #include "common.cuh"
@@ -27,15 +37,14 @@ namespace w4ts {
 
 constexpr int kRows = 128;           // weight rows per tile (UMMA M, TMEM lanes)
 constexpr int kTok = 128;            // tokens per tile (UMMA N)
-constexpr int kGroup = 128;          // K per scale group
-constexpr int kBK = 64;              // K per stage: one 128-byte swizzle row of bf16 activations; two stages per group
-constexpr int kXBytes = kTok * 128;  // 16 KiB per stage
-constexpr int kMaxLoadStages = 12;
-constexpr int kASlots = 8;           // ring of converted weight tiles in tensor memory, 32 columns each
+constexpr int kGroup = 128;          // K per scale group = K per pipeline step
+constexpr int kBoxBytes = kTok * 128;        // one 64-K box of activations, 16 KiB
+constexpr int kXBytes = 2 * kBoxBytes;       // 32 KiB per step
+constexpr int kMaxLoadStages = 6;
+constexpr int kASlots = 4;           // ring of converted weight tiles in tensor memory, 64 columns each
 constexpr int kFoldWarps = 8, kTeamWarps = 4;
-constexpr uint32_t kTmemCols = 512;  // two accumulators of 128 columns + 8 x 32 columns of weights
-constexpr int kBarBytes = 512;
-constexpr int kAhead = 2;            // how many of its own stages a converter requests its bytes ahead
+constexpr uint32_t kTmemCols = 512;  // two accumulators of 128 columns + 4 x 64 columns of weights
+constexpr int kBarBytes = 256;
 
 struct Params {
     const __nv_bfloat16* X;
@@ -56,8 +65,26 @@ __device__ __forceinline__ uint32_t sub136(uint32_t v)
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-template <int TEAMS>
-__global__ void __launch_bounds__(32 * (2 + kFoldWarps + kTeamWarps * TEAMS), 1)
+// Eight packed words (64 weights of one row) -> 32 words of bf16 pairs in ascending K.
+__device__ __forceinline__ void convert64(const uint4& lo, const uint4& hi, uint32_t (&r)[32])
+{
+    const uint32_t ww[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {                      // word j: K offsets 8 j .. 8 j + 7
+        // nibble pairs (i, i + 4) as bf16 integers 136 + q by one logic operation ((w & mask) ^ const flips the sign
+        // bit of the nibble and sets the exponent), minus 136 exactly, then pairs of ascending K by byte permutes
+        const uint32_t a0 = sub136((ww[j] & 0x000F000Fu) ^ 0x43084308u);
+        const uint32_t a1 = sub136(((ww[j] >> 4) & 0x000F000Fu) ^ 0x43084308u);
+        const uint32_t a2 = sub136(((ww[j] >> 8) & 0x000F000Fu) ^ 0x43084308u);
+        const uint32_t a3 = sub136(((ww[j] >> 12) & 0x000F000Fu) ^ 0x43084308u);
+        r[4 * j + 0] = __byte_perm(a0, a1, 0x5410);
+        r[4 * j + 1] = __byte_perm(a2, a3, 0x5410);
+        r[4 * j + 2] = __byte_perm(a0, a1, 0x7632);
+        r[4 * j + 3] = __byte_perm(a2, a3, 0x7632);
+    }
+}
+
+__global__ void __launch_bounds__(32 * (2 + kFoldWarps + kTeamWarps), 1)
 w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -66,24 +93,22 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
     const int LS = p.load_stages;
     auto x_tile = [&](int s) { return smem_base + s * kXBytes; };
     const uint32_t bar_base = smem_base + LS * kXBytes;
-    auto full_bar = [&](int s) { return bar_base + 8u * s; };                            // the activation tile has landed
-    auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxLoadStages + s); };        // ... and the MMAs that read it retired
-    auto aready_bar = [&](int a) { return bar_base + 8u * (2 * kMaxLoadStages + a); };   // the A slot holds converted weights
-    auto afree_bar = [&](int a) { return bar_base + 8u * (2 * kMaxLoadStages + kASlots + a); };
-    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kMaxLoadStages + 2 * kASlots + b); };
-    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxLoadStages + 2 * kASlots + 2 + b); };
-    const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxLoadStages + 2 * kASlots + 4);
+    auto xfull_bar = [&](int s) { return bar_base + 8u * s; };                          // the activation tile has landed
+    auto xempty_bar = [&](int s) { return bar_base + 8u * (kMaxLoadStages + s); };      // ... and the MMAs that read it retired
+    auto aready_bar = [&](int a) { return bar_base + 8u * (2 * kMaxLoadStages + a); };  // the A slot holds converted weights
+    auto done_bar = [&](int a) { return bar_base + 8u * (2 * kMaxLoadStages + kASlots + a); };   // the group's MMAs retired
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kMaxLoadStages + 2 * kASlots + b); };
+    const uint32_t tmem_slot = bar_base + 8u * (2 * kMaxLoadStages + 2 * kASlots + 2);
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int G = p.K / kGroup;
-    const int spt = p.K / kBK;                               // stages per tile, two per group
+    const int G = p.K / kGroup;                              // pipeline steps per tile
     const int num_tiles = p.tiles_m * p.tiles_n;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < LS; ++s) { ptx::mbar_init(full_bar(s), 1); ptx::mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < kASlots; ++a) { ptx::mbar_init(aready_bar(a), kTeamWarps); ptx::mbar_init(afree_bar(a), 1); }
-        for (int b = 0; b < 2; ++b) { ptx::mbar_init(tfull_bar(b), 1); ptx::mbar_init(tempty_bar(b), kFoldWarps); }
+        for (int s = 0; s < LS; ++s) { ptx::mbar_init(xfull_bar(s), 1); ptx::mbar_init(xempty_bar(s), 1); }
+        for (int a = 0; a < kASlots; ++a) { ptx::mbar_init(aready_bar(a), kTeamWarps); ptx::mbar_init(done_bar(a), 1); }
+        for (int b = 0; b < 2; ++b) ptx::mbar_init(tempty_bar(b), kFoldWarps);
         ptx::fence_mbar_init();
     }
     if (warp == 1) { ptx::tmem_alloc(tmem_slot, kTmemCols); ptx::tmem_relinquish(); }
@@ -100,10 +125,11 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
             int stage = 0; uint32_t phase = 0; bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 const int m0 = (tile / p.tiles_n) * kTok;
-                for (int i = 0; i < spt; ++i) {
-                    if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, p.status, 41)) { ok = false; break; }
-                    ptx::mbar_arrive_expect_tx(full_bar(stage), kXBytes);
-                    ptx::tma_load_2d(x_tile(stage), &tmX, full_bar(stage), i * kBK, m0);
+                for (int g = 0; g < G; ++g) {
+                    if (!ptx::mbar_wait(xempty_bar(stage), phase ^ 1u, p.status, 41)) { ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(xfull_bar(stage), kXBytes);
+                    ptx::tma_load_2d(x_tile(stage), &tmX, xfull_bar(stage), g * kGroup, m0);
+                    ptx::tma_load_2d(x_tile(stage) + kBoxBytes, &tmX, xfull_bar(stage), g * kGroup + 64, m0);
                     if (++stage == LS) { stage = 0; phase ^= 1u; }
                 }
             }
@@ -115,29 +141,24 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
             // bf16 x bf16 -> fp32, both K-major; M = 128 weight rows (A, tensor memory), N = 128 tokens (B, shared memory)
             constexpr uint32_t idesc = ptx::umma_idesc(1, 1, kRows, kTok);
             int stage = 0; uint32_t phase = 0; bool ok = true;
-            int slot = 0; uint32_t aphase = 0;
             int gi = 0;                                             // groups issued so far (over all tiles)
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                for (int g = 0; g < G && ok; ++g, ++gi) {
-                    const int buf = gi & 1;
-                    if (!ptx::mbar_wait(tempty_bar(buf), ((gi >> 1) & 1u) ^ 1u, p.status, 42)) { ok = false; break; }
+                for (int g = 0; g < G; ++g, ++gi) {
+                    const int buf = gi & 1, slot = gi & (kASlots - 1);
+                    if (!ptx::mbar_wait(tempty_bar(buf), ((gi >> 1) & 1u) ^ 1u, p.status, 42) ||
+                        !ptx::mbar_wait(xfull_bar(stage), phase, p.status, 43) ||
+                        !ptx::mbar_wait(aready_bar(slot), (gi / kASlots) & 1u, p.status, 44)) { ok = false; break; }
                     ptx::tcgen05_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + buf * kTok;
-                    for (int h = 0; h < 2; ++h) {
-                        if (!ptx::mbar_wait(full_bar(stage), phase, p.status, 43) ||
-                            !ptx::mbar_wait(aready_bar(slot), aphase, p.status, 44)) { ok = false; break; }
-                        ptx::tcgen05_fence_after_sync();
-                        const uint64_t db = ptx::smem_desc_sw128_kmajor(x_tile(stage));
-                        const uint32_t a_tmem = a_tmem0 + slot * 32;
+                    const uint32_t a_tmem = a_tmem0 + slot * 64;
+                    const uint64_t db0 = ptx::smem_desc_sw128_kmajor(x_tile(stage));
+                    const uint64_t db1 = ptx::smem_desc_sw128_kmajor(x_tile(stage) + kBoxBytes);
 #pragma unroll
-                        for (int k = 0; k < kBK / 16; ++k)          // 16 K: 8 columns of A, 32 bytes of B (+2 in 16-byte units)
-                            ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k, db + 2u * k, idesc, (h | k) != 0);
-                        ptx::umma_commit(empty_bar(stage));
-                        ptx::umma_commit(afree_bar(slot));
-                        if (++stage == LS) { stage = 0; phase ^= 1u; }
-                        if (++slot == kASlots) { slot = 0; aphase ^= 1u; }
-                    }
-                    if (ok) ptx::umma_commit(tfull_bar(buf));
+                    for (int k = 0; k < 8; ++k)                     // 16 K: 8 columns of A, 32 bytes of B (+2 in 16-byte units)
+                        ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k, (k < 4 ? db0 : db1) + 2u * (k & 3), idesc, k != 0);
+                    ptx::umma_commit(done_bar(slot));               // converters: the slot is free; fold: the sum is complete
+                    ptx::umma_commit(xempty_bar(stage));
+                    if (++stage == LS) { stage = 0; phase ^= 1u; }
                 }
             }
             if (!ok) __nanosleep(200000);
@@ -160,8 +181,8 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
             for (int g = 0; g < G && ok; ++g, ++gi) {
                 const float s = s_next;
                 if (g + 1 < G) s_next = (n < p.N) ? __half2float(__ldg(srow + g + 1)) : 0.0f;
-                const int buf = gi & 1;
-                if (!ptx::mbar_wait(tfull_bar(buf), (gi >> 1) & 1u, p.status, 45)) { ok = false; break; }
+                const int buf = gi & 1, slot = gi & (kASlots - 1);
+                if (!ptx::mbar_wait(done_bar(slot), (gi / kASlots) & 1u, p.status, 45)) { ok = false; break; }
                 ptx::tcgen05_fence_after_sync();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kTok + 64 * half;
 #pragma unroll
@@ -169,14 +190,16 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
                     uint32_t d[16];
                     ptx::tmem_ld_32x32b_x16(taddr + 16 * c, d);
                     ptx::tmem_ld_wait();
+                    if (c == 3) {                                 // all of it is in registers: hand the accumulator back before the arithmetic
+                        ptx::tcgen05_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
+                    }
 #pragma unroll
                     for (int i = 0; i < 8; ++i)                    // fma.rn.f32x2: the same roundings as two scalar FMAs
                         acc[8 * c + i] = __ffma2_rn(make_float2(__uint_as_float(d[2 * i]), __uint_as_float(d[2 * i + 1])),
                                                     make_float2(s, s), acc[8 * c + i]);
                 }
-                ptx::tcgen05_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(tempty_bar(buf));
             }
             // one rounding to bf16; the tile is transposed: a warp's lanes are 32 consecutive output columns of one token
             if (ok && n < p.N) {
@@ -190,60 +213,45 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
         }
     } else {
         // ---------------------------------------------------------------- converters: packed int4 -> bf16 A tile in TMEM
-        const int ct = threadIdx.x - 32 * (2 + kFoldWarps);
-        const int team = ct >> 7;
         const int row = (warp & 3) * 32 + lane;                  // TMEM lane this warp may write = weight row in the tile
         const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const size_t row_bytes = static_cast<size_t>(p.K) / 2;
-        // position of the bytes requested ahead: (tile, stage in tile), advanced by TEAMS stages at a time
-        int pf_tile = blockIdx.x, pf_k = team;
-        auto pf_norm = [&]() { while (pf_k >= spt) { pf_k -= spt; pf_tile += gridDim.x; } };
-        auto pf_load = [&](uint4& lo, uint4& hi) {
-            pf_norm();
+        // position of the bytes requested ahead: (tile, group in tile)
+        int pf_tile = blockIdx.x, pf_g = 0;
+        auto pf_load = [&](uint4 (&w)[4]) {
+            while (pf_g >= G) { pf_g -= G; pf_tile += gridDim.x; }
             const int n = (pf_tile % p.tiles_n) * kRows + row;
             if (pf_tile < num_tiles && n < p.N) {
-                const uint4* src = reinterpret_cast<const uint4*>(p.Wq + static_cast<size_t>(n) * row_bytes + static_cast<size_t>(pf_k) * (kBK / 2));
-                lo = __ldg(src); hi = __ldg(src + 1);
+                const uint4* src = reinterpret_cast<const uint4*>(p.Wq + static_cast<size_t>(n) * row_bytes + static_cast<size_t>(pf_g) * (kGroup / 2));
+#pragma unroll
+                for (int i = 0; i < 4; ++i) w[i] = __ldg(src + i);
             } else {
-                lo = make_uint4(0, 0, 0, 0); hi = lo;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) w[i] = make_uint4(0, 0, 0, 0);
             }
-            pf_k += TEAMS;
+            pf_g += 1;
         };
-        uint4 wlo[kAhead + 1], whi[kAhead + 1];
-#pragma unroll
-        for (int a = 0; a < kAhead; ++a) pf_load(wlo[a], whi[a]);
+        uint4 wcur[4], wnext[4];
+        pf_load(wcur);
         bool ok = true;
-        int it = 0;                                              // running stage index over all tiles
+        int gi = 0;                                              // running group index over all tiles
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            for (int i = 0; i < spt; ++i, ++it) {
-                if (TEAMS > 1 && (it % TEAMS) != team) continue;
-                const int slot = it % kASlots;
-                const uint32_t aphase = (it / kASlots) & 1u;
-                pf_load(wlo[kAhead], whi[kAhead]);
-                if (!ptx::mbar_wait(afree_bar(slot), aphase ^ 1u, p.status, 46)) { ok = false; break; }
+            for (int g = 0; g < G; ++g, ++gi) {
+                const int slot = gi & (kASlots - 1);
+                pf_load(wnext);
+                if (!ptx::mbar_wait(done_bar(slot), ((gi / kASlots) & 1u) ^ 1u, p.status, 46)) { ok = false; break; }
                 ptx::tcgen05_fence_after_sync();
-                const uint32_t ww[8] = {wlo[0].x, wlo[0].y, wlo[0].z, wlo[0].w, whi[0].x, whi[0].y, whi[0].z, whi[0].w};
                 uint32_t r[32];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {                      // word j: K offsets 8 j .. 8 j + 7 of this stage
-                    // nibble pairs (i, i + 4) as bf16 integers 136 + q by one logic operation ((w & mask) ^ const flips the
-                    // sign bit of the nibble and sets the exponent), minus 136 exactly, then pairs of ascending K
-                    const uint32_t a0 = sub136((ww[j] & 0x000F000Fu) ^ 0x43084308u);
-                    const uint32_t a1 = sub136(((ww[j] >> 4) & 0x000F000Fu) ^ 0x43084308u);
-                    const uint32_t a2 = sub136(((ww[j] >> 8) & 0x000F000Fu) ^ 0x43084308u);
-                    const uint32_t a3 = sub136(((ww[j] >> 12) & 0x000F000Fu) ^ 0x43084308u);
-                    r[4 * j + 0] = __byte_perm(a0, a1, 0x5410);
-                    r[4 * j + 1] = __byte_perm(a2, a3, 0x5410);
-                    r[4 * j + 2] = __byte_perm(a0, a1, 0x7632);
-                    r[4 * j + 3] = __byte_perm(a2, a3, 0x7632);
-                }
-                ptx::tmem_st_32x32b_x32(a_tmem0 + lane_addr + slot * 32, r);
+                convert64(wcur[0], wcur[1], r);
+                ptx::tmem_st_32x32b_x32(a_tmem0 + lane_addr + slot * 64, r);
+                convert64(wcur[2], wcur[3], r);
+                ptx::tmem_st_32x32b_x32(a_tmem0 + lane_addr + slot * 64 + 32, r);
                 ptx::tmem_st_wait();
                 ptx::tcgen05_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(aready_bar(slot));
 #pragma unroll
-                for (int a = 0; a < kAhead; ++a) { wlo[a] = wlo[a + 1]; whi[a] = whi[a + 1]; }
+                for (int i = 0; i < 4; ++i) wcur[i] = wnext[i];
             }
         }
     }
@@ -261,9 +269,6 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
 
 namespace b200q {
 
-int g_prefill_ts_teams = 2, g_prefill_ts_depth = 8;
-extern "C" int b200q_w4a16_prefill_ts_debug(int teams, int depth) { g_prefill_ts_teams = teams; g_prefill_ts_depth = depth; return 0; }
-
 // Called by b200q_gemm_w4a16 for more than 16 tokens (K a multiple of 128).
 int gemm_w4a16_prefill_ts(const void* X, const void* Wq, const void* S, void* Y, int M, int N, int K, int group, void* stream)
 {
@@ -276,14 +281,14 @@ int gemm_w4a16_prefill_ts(const void* X, const void* Wq, const void* S, void* Y,
     p.S = static_cast<const __half*>(S); p.Y = static_cast<__nv_bfloat16*>(Y);
     p.M = M; p.N = N; p.K = K;
     p.tiles_m = (M + kTok - 1) / kTok; p.tiles_n = (N + kRows - 1) / kRows;
-    p.load_stages = g_prefill_ts_depth < 2 ? 2 : (g_prefill_ts_depth > kMaxLoadStages ? kMaxLoadStages : g_prefill_ts_depth);
+    p.load_stages = kMaxLoadStages;
     p.status = status_ptr();
     if (p.status == nullptr) return cudaErrorInvalidDevice;
     CUtensorMap tmX;
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
         const uint64_t strides[1] = {static_cast<uint64_t>(K) * 2};
-        const uint32_t box[2] = {kBK, kTok};
+        const uint32_t box[2] = {64, kTok};
         if (encode_tiled(&tmX, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, X, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B) != CUDA_SUCCESS)
             return cudaErrorInvalidValue;
     }
@@ -293,17 +298,16 @@ int gemm_w4a16_prefill_ts(const void* X, const void* Wq, const void* S, void* Y,
     const int tiles = p.tiles_m * p.tiles_n;
     const int grid = tiles < sms ? tiles : sms;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define B200Q_PREFILL_TS(TEAMS_)                                                                                          \
-    do {                                                                                                                   \
-        auto kern = w4a16_prefill_ts_kernel<TEAMS_>;                                                                       \
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 + kBarBytes + kMaxLoadStages * kXBytes); \
-        if (e != cudaSuccess) return e;                                                                                    \
-        kern<<<grid, 32 * (2 + kFoldWarps + kTeamWarps * TEAMS_), smem_bytes, st>>>(tmX, p);                               \
-    } while (0)
-    if (g_prefill_ts_teams >= 3) B200Q_PREFILL_TS(3);
-    else if (g_prefill_ts_teams == 2) B200Q_PREFILL_TS(2);
-    else B200Q_PREFILL_TS(1);
-#undef B200Q_PREFILL_TS
+    static bool configured[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 64 && !configured[dev]) {
+        e = cudaFuncSetAttribute(w4a16_prefill_ts_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        if (e != cudaSuccess) return e;
+        configured[dev] = true;
+    }
+    w4a16_prefill_ts_kernel<<<grid, 32 * (2 + kFoldWarps + kTeamWarps), smem_bytes, st>>>(tmX, p);
     return cudaGetLastError();
 }
 

@@ -154,12 +154,13 @@ int b200q_nvfp4_set_tile_n(int bn);
 int b200q_nvfp4_set_2cta(int on);      /* NVFP4 GEMM on CTA pairs (256 x 192 / 256 x 256 tiles per pair) when M > 128 and the
                                         * tile width is not 128; default on */
 int b200q_w4a16_set_impl(int impl);     /* 0 = by M (default): streaming CUDA-core GEMV for one token (the older GEMV forms when K is not
-                                         * a multiple of 2048 or exceeds 16384), warp-MMA kernel for 2..16 tokens, tcgen05
-                                         * prefill kernel (group-wise partial-sum scaling) above 16; 5 / 6 = the streaming
-                                         * GEMV / the prefill kernel wherever they apply; 7 = the prefill kernel whose
-                                         * converters subtract the integer offset themselves; 8 = the prefill kernel that
-                                         * keeps the converted weights in tensor memory (product computed transposed);
-                                         * 1 = tcgen05 kernel; 2 = warp-MMA kernel for every M; 3 / 4 = the two GEMV forms
+                                         * a multiple of 2048 or exceeds 16384), warp-MMA kernel for 2..16 tokens, above 16 the
+                                         * tcgen05 prefill kernel that keeps the converted weights in tensor memory (group-wise
+                                         * partial-sum scaling, product computed transposed);
+                                         * 5 / 8 = the streaming GEMV / that prefill kernel wherever they apply;
+                                         * 6 / 7 = the prefill kernel that converts through shared memory (the integer offset taken
+                                         * out by rows of ones / by the converters);
+                                         * 1 = tcgen05 decode kernel; 2 = warp-MMA kernel for every M; 3 / 4 = the two GEMV forms
                                          * (shared memory + dp4a / registers + fp32) for up to 4 tokens */
 int b200q_w4a16_set_pdl(int on);        /* programmatic dependent launch of the GEMV / tcgen05 W4A16 kernels (default off):
                                          * the call may start streaming its weights while the previous kernel of the stream
