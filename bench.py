@@ -573,6 +573,10 @@ def run_ours(args):
     ms_e2e = timed(e2e_step, args.steps, args.warmup, finish=e2e_finish)
     clocks = sampler.stop() if sampler else None
     assert ops.status() == 0, "a kernel gave up on a bounded wait"
+    # what the host-fed steps left in pinned memory (this rank's rows) against a plain device-resident forward
+    mlp.cancel_prepared()
+    y_dev = mlp.forward(x); mlp.wait(); torch.cuda.synchronize()
+    e2e_rows_equal = bool(torch.equal(y_host[fed.lo:fed.hi], y_dev[fed.lo:fed.hi].cpu()))
     parity = multi_rank_parity(mlp, x, rank, world, dev) if world > 1 else None
 
     if rank != 0:
@@ -600,6 +604,7 @@ def run_ours(args):
         "clocks": clocks,
         "e2e": {"value": TOKENS / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": TOKENS * HIDDEN * 2, "d2h_bytes_per_step": TOKENS * HIDDEN * 2,
+                "result_rows_equal_device_run": e2e_rows_equal,
                 "note": "whole-job bytes per step through cudaop_b200.mlp.HostFedMLP; copies run on their own streams, "
                         "double-buffered, overlapping the GEMMs of the neighbouring steps; with R ranks each rank copies "
                         "1/R of X in and 1/R of Y out over its own PCIe link and pulls the rest of X from its peers "

@@ -555,7 +555,7 @@ class HostFedMLP:
         y = mlp.forward(self.xbuf[b][:self.tokens])
         done = torch.cuda.Event(); done.record(main)
         self._x_free[b] = done
-        side = mlp.comm_stream if (self.world > 1 and mlp.comm == "pipelined") else self.copy_out
+        side = mlp.comm_stream if (self.world > 1 and mlp.comm.startswith("pipelined")) else self.copy_out
         with torch.cuda.stream(side):                 # ordered after this step's GEMMs (and its all-reduce)
             side.wait_event(done)
             y_host[lo:hi].copy_(y[lo:hi], non_blocking=True)

@@ -41,6 +41,16 @@ def _worker(rank, world, port, mode, pdt, out_dir):
     torch.cuda.synchronize()
     assert ops.status() == 0
     assert torch.equal(y, y2)
+    # the host-fed pipeline on top of the same layer: this rank's rows of the result arrive in pinned memory
+    from cudaop_b200.mlp import HostFedMLP
+    fed = HostFedMLP(mlp, T)
+    x_host = x.cpu().pin_memory()
+    y_host = torch.zeros((T, H), dtype=torch.bfloat16).pin_memory()
+    for _ in range(3):
+        fed.step(x_host, y_host)
+    fed.finish(); torch.cuda.synchronize()
+    assert ops.status() == 0
+    assert torch.equal(y_host[fed.lo:fed.hi], y[fed.lo:fed.hi].cpu())
     # the kernel's sum against the fp32 partials of both ranks gathered with NCCL
     if mode == "nccl":
         # NCCL reduced mlp.partial in place: rebuild this rank's own partial with the stand-alone down projection

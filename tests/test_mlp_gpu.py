@@ -130,3 +130,25 @@ def test_prepare_quantises_the_next_batch_ahead_with_the_same_bits():
     assert torch.equal(y2, y2_plain) and mlp._prep is not None
     mlp.cancel_prepared()
     assert mlp._prep is None and ops.status() == 0
+
+
+@pytest.mark.parametrize("prepare_ahead", [True, False])
+def test_host_fed_pipeline_leaves_the_result_in_pinned_memory(prepare_ahead):
+    """HostFedMLP on one rank: inputs from pinned host memory, double-buffered copies on their own streams, the result
+    back in pinned memory -- the same bits as a device-resident forward, for more steps than buffers."""
+    from cudaop_b200.mlp import HostFedMLP, TensorParallelMLP
+    import cudaop_b200 as ops
+    T, H, I = 192, 512, 1024
+    case = oracle.make_mlp_case(T, H, I, seed=17)
+    mlp = TensorParallelMLP(*_tensors(case), max_tokens=T)
+    x = dev(case[0], torch.bfloat16)
+    want = mlp(x).clone().cpu()
+    fed = HostFedMLP(mlp, T, prepare_ahead=prepare_ahead)
+    xs = [x.cpu().pin_memory(), (x.float() * 0.5).to(torch.bfloat16).cpu().pin_memory()]
+    want2 = mlp(xs[1].cuda()).clone().cpu()
+    y_host = [torch.zeros((T, H), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    for i in range(5):
+        fed.step(xs[i & 1], y_host[i & 1])
+    fed.finish(); torch.cuda.synchronize()
+    assert ops.status() == 0
+    assert torch.equal(y_host[0], want) and torch.equal(y_host[1], want2)
