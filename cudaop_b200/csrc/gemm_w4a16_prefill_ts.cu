@@ -11,17 +11,20 @@
 //   warps 10..   converters, one thread per weight row and TMEM lane: the row's 64 packed bytes of the group straight
 //                from global memory (requested one group ahead), nibble pairs -> bf16 integers by one
 //                logic operation and one exact subtraction per pair, re-paired by byte permutes, two tcgen05.st of 32
-//                columns into a ring of four A slots.
+//                columns into a ring of four A slots.  Two teams of four warps take alternate groups; each keeps
+//                two register sets for the packed bytes and alternates between them.
 //   warp 1       MMA issuer: 8 x tcgen05.mma kind::f16 (A from tensor memory, 128 x 128 x 16) into one of two
 //                accumulators, then ONE commit that tells the converters (A slot free) and the fold warps
 //                (accumulator complete), and one for the producer.
-// What sets the pace (timestamps written from inside the kernel, 4096^3): a group's eight MMAs take about 0.7 us
-// from commit to completion, 2.5 times their arithmetic: each 128 x 128 x 16 MMA adds to the accumulator the one
-// before it wrote, and 64 clocks of arithmetic do not cover that dependency.  Wider MMAs would, but two 256-column
-// accumulators and the weights do not fit the 512 columns of tensor memory together, and every group's accumulator
-// has to be read out for its scale.  A second team of converters, a second issuing thread, a deeper activation ring
-// and another tile order were measured and changed nothing beyond a few percent; 64-K steps were 25 % slower (the
-// issuing thread's chain of waits and commits per step).
+// What sets the pace (timestamps written from inside the kernel, and the probe bench/tcgen05_mma_rate.cu): a
+// 128 x 128 x 16 MMA with A in tensor memory retires every 93 clocks whatever accumulator it adds to (69 % of the
+// dense rate; 128 x 256 x 16: 139 clocks, 92 %), and inside this kernel, beside the converters' tcgen05.st and the
+// fold's tcgen05.ld, a group's eight take about twice that.  Wider MMAs are out of reach: two 256-column accumulators
+// and the weights do not fit the 512 columns of tensor memory, and every group's accumulator has to be read out for
+// its scale.  Measured along the way: 64-K steps were 25 % slower (the issuing thread's chain of waits and commits per
+// step); copying the prefetched bytes into a "current" register set cost 0.3 us per group (the copy waits for the
+// loads): two sets used alternately, +17 %; a second converter team on top, +15 %; a second issuing thread, a deeper
+// activation ring, another tile order and an epilogue staged through shared memory changed nothing.
 //   warps 2-9    fold: tcgen05.ld the group's accumulator and add s[n, g] * acc into fp32 registers -- the scale is
 //                one scalar per thread and group (lane = weight row); after the last group: bf16, stored transposed.
 // Against the form that converts through shared memory (gemm_w4a16_prefill.cu) a group moves 80 KB less through
@@ -84,7 +87,8 @@ __device__ __forceinline__ void convert64(const uint4& lo, const uint4& hi, uint
     }
 }
 
-__global__ void __launch_bounds__(32 * (2 + kFoldWarps + kTeamWarps), 1)
+constexpr int kTeams = 2;          // converter teams: measured 15-20 % over one
+__global__ void __launch_bounds__(32 * (2 + kFoldWarps + kTeamWarps * kTeams), 1)
 w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -140,26 +144,23 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
         if (ptx::elect_one()) {
             // bf16 x bf16 -> fp32, both K-major; M = 128 weight rows (A, tensor memory), N = 128 tokens (B, shared memory)
             constexpr uint32_t idesc = ptx::umma_idesc(1, 1, kRows, kTok);
-            int stage = 0; uint32_t phase = 0; bool ok = true;
-            int gi = 0;                                             // groups issued so far (over all tiles)
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                for (int g = 0; g < G; ++g, ++gi) {
-                    const int buf = gi & 1, slot = gi & (kASlots - 1);
-                    if (!ptx::mbar_wait(tempty_bar(buf), ((gi >> 1) & 1u) ^ 1u, p.status, 42) ||
-                        !ptx::mbar_wait(xfull_bar(stage), phase, p.status, 43) ||
-                        !ptx::mbar_wait(aready_bar(slot), (gi / kASlots) & 1u, p.status, 44)) { ok = false; break; }
-                    ptx::tcgen05_fence_after_sync();
-                    const uint32_t d_tmem = tmem_base + buf * kTok;
-                    const uint32_t a_tmem = a_tmem0 + slot * 64;
-                    const uint64_t db0 = ptx::smem_desc_sw128_kmajor(x_tile(stage));
-                    const uint64_t db1 = ptx::smem_desc_sw128_kmajor(x_tile(stage) + kBoxBytes);
+            const int total = ((num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)) * G;
+            bool ok = true;
+            for (int gi = 0; gi < total && ok; ++gi) {               // running group index over all tiles of this CTA
+                const int buf = gi & 1, slot = gi & (kASlots - 1), stage = gi % LS;
+                if (!ptx::mbar_wait(tempty_bar(buf), ((gi >> 1) & 1u) ^ 1u, p.status, 42) ||
+                    !ptx::mbar_wait(xfull_bar(stage), (gi / LS) & 1u, p.status, 43) ||
+                    !ptx::mbar_wait(aready_bar(slot), (gi / kASlots) & 1u, p.status, 44)) { ok = false; break; }
+                ptx::tcgen05_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buf * kTok;
+                const uint32_t a_tmem = a_tmem0 + slot * 64;
+                const uint64_t db0 = ptx::smem_desc_sw128_kmajor(x_tile(stage));
+                const uint64_t db1 = ptx::smem_desc_sw128_kmajor(x_tile(stage) + kBoxBytes);
 #pragma unroll
-                    for (int k = 0; k < 8; ++k)                     // 16 K: 8 columns of A, 32 bytes of B (+2 in 16-byte units)
-                        ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k, (k < 4 ? db0 : db1) + 2u * (k & 3), idesc, k != 0);
-                    ptx::umma_commit(done_bar(slot));               // converters: the slot is free; fold: the sum is complete
-                    ptx::umma_commit(xempty_bar(stage));
-                    if (++stage == LS) { stage = 0; phase ^= 1u; }
-                }
+                for (int k = 0; k < 8; ++k)                         // 16 K: 8 columns of A, 32 bytes of B (+2 in 16-byte units)
+                    ptx::umma_f16_ts(d_tmem, a_tmem + 8 * k, (k < 4 ? db0 : db1) + 2u * (k & 3), idesc, k != 0);
+                ptx::umma_commit(done_bar(slot));                   // converters: the slot is free; fold: the sum is complete
+                ptx::umma_commit(xempty_bar(stage));
             }
             if (!ok) __nanosleep(200000);
         }
@@ -213,11 +214,12 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
         }
     } else {
         // ---------------------------------------------------------------- converters: packed int4 -> bf16 A tile in TMEM
+        const int team = (warp - 2 - kFoldWarps) >> 2;
         const int row = (warp & 3) * 32 + lane;                  // TMEM lane this warp may write = weight row in the tile
         const uint32_t lane_addr = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const size_t row_bytes = static_cast<size_t>(p.K) / 2;
         // position of the bytes requested ahead: (tile, group in tile)
-        int pf_tile = blockIdx.x, pf_g = 0;
+        int pf_tile = blockIdx.x, pf_g = team;
         auto pf_load = [&](uint4 (&w)[4]) {
             while (pf_g >= G) { pf_g -= G; pf_tile += gridDim.x; }
             const int n = (pf_tile % p.tiles_n) * kRows + row;
@@ -229,30 +231,32 @@ w4a16_prefill_ts_kernel(const __grid_constant__ CUtensorMap tmX, const Params p)
 #pragma unroll
                 for (int i = 0; i < 4; ++i) w[i] = make_uint4(0, 0, 0, 0);
             }
-            pf_g += 1;
+            pf_g += kTeams;
         };
-        uint4 wcur[4], wnext[4];
-        pf_load(wcur);
-        bool ok = true;
-        int gi = 0;                                              // running group index over all tiles
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-            for (int g = 0; g < G; ++g, ++gi) {
-                const int slot = gi & (kASlots - 1);
-                pf_load(wnext);
-                if (!ptx::mbar_wait(done_bar(slot), ((gi / kASlots) & 1u) ^ 1u, p.status, 46)) { ok = false; break; }
-                ptx::tcgen05_fence_after_sync();
-                uint32_t r[32];
-                convert64(wcur[0], wcur[1], r);
-                ptx::tmem_st_32x32b_x32(a_tmem0 + lane_addr + slot * 64, r);
-                convert64(wcur[2], wcur[3], r);
-                ptx::tmem_st_32x32b_x32(a_tmem0 + lane_addr + slot * 64 + 32, r);
-                ptx::tmem_st_wait();
-                ptx::tcgen05_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(aready_bar(slot));
-#pragma unroll
-                for (int i = 0; i < 4; ++i) wcur[i] = wnext[i];
-            }
+        // Two register sets used alternately (the loop is unrolled by two): copying "next" into "current" at the
+        // end of a step would wait for the loads just issued, 0.3 us measured per group.
+        uint4 wa[4], wb[4];
+        pf_load(wa);
+        const int total = ((num_tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)) * G;
+        auto step = [&](const uint4 (&cur)[4], uint4 (&nxt)[4], int gi) -> bool {
+            const int slot = gi & (kASlots - 1);
+            pf_load(nxt);
+            if (!ptx::mbar_wait(done_bar(slot), ((gi / kASlots) & 1u) ^ 1u, p.status, 46)) return false;
+            ptx::tcgen05_fence_after_sync();
+            uint32_t r[32];
+            convert64(cur[0], cur[1], r);
+            ptx::tmem_st_32x32b_x32(a_tmem0 + lane_addr + slot * 64, r);
+            convert64(cur[2], cur[3], r);
+            ptx::tmem_st_32x32b_x32(a_tmem0 + lane_addr + slot * 64 + 32, r);
+            ptx::tmem_st_wait();
+            ptx::tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(aready_bar(slot));
+            return true;
+        };
+        for (int gi = team; gi < total; gi += 2 * kTeams) {       // running group index over all tiles of this CTA
+            if (!step(wa, wb, gi)) break;
+            if (gi + kTeams < total && !step(wb, wa, gi + kTeams)) break;
         }
     }
 
@@ -307,7 +311,7 @@ int gemm_w4a16_prefill_ts(const void* X, const void* Wq, const void* S, void* Y,
         if (e != cudaSuccess) return e;
         configured[dev] = true;
     }
-    w4a16_prefill_ts_kernel<<<grid, 32 * (2 + kFoldWarps + kTeamWarps), smem_bytes, st>>>(tmX, p);
+    w4a16_prefill_ts_kernel<<<grid, 32 * (2 + kFoldWarps + kTeamWarps * kTeams), smem_bytes, st>>>(tmX, p);
     return cudaGetLastError();
 }
 
