@@ -509,6 +509,9 @@ class HostFedMLP:
         self.lo, self.hi = self.rank * self.rows, (self.rank + 1) * self.rows
         self.copy_in, self.copy_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         self._x_free = [None, None]     # event: the forward that last read X buffer b has been issued
+        self._y_read = [None, None]     # event: the copy-out that last read output buffer b has finished
+        self._ybuf = ([torch.empty((tokens, H), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+                      if self.world == 1 else None)
         self._step = 0
         self._epoch = 0
         if self.world == 1:
@@ -552,13 +555,26 @@ class HostFedMLP:
         main.wait_event(ready)
         if self.prepare_ahead:                         # quantise X beside the previous step's GEMMs
             mlp.prepare(self.xbuf[b][:self.tokens], ready=ready)
-        y = mlp.forward(self.xbuf[b][:self.tokens])
+        pipelined = self.world > 1 and mlp.comm.startswith("pipelined")
+        if self.world == 1:
+            # the layer writes into one of two buffers of this object, not before the copy-out that last read it is done
+            if self._y_read[b] is not None:
+                main.wait_event(self._y_read[b])
+            y = mlp.forward(self.xbuf[b][:self.tokens], out=self._ybuf[b])
+        else:
+            # the pipelined modes alternate between two output buffers and order the copy-out themselves (it runs
+            # on the exchange's stream); the others have ONE output buffer: the next forward waits for the copy-out
+            if not pipelined and self._y_read[0] is not None:
+                main.wait_event(self._y_read[0])
+            y = mlp.forward(self.xbuf[b][:self.tokens])
         done = torch.cuda.Event(); done.record(main)
         self._x_free[b] = done
-        side = mlp.comm_stream if (self.world > 1 and mlp.comm.startswith("pipelined")) else self.copy_out
+        side = mlp.comm_stream if pipelined else self.copy_out
         with torch.cuda.stream(side):                 # ordered after this step's GEMMs (and its all-reduce)
             side.wait_event(done)
             y_host[lo:hi].copy_(y[lo:hi], non_blocking=True)
+            read = torch.cuda.Event(); read.record(side)
+        self._y_read[b if self.world == 1 else 0] = read
 
     def finish(self):
         main = torch.cuda.current_stream()
