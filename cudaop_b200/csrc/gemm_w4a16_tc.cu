@@ -342,8 +342,8 @@ w4a16_tc_kernel(const __grid_constant__ CUtensorMap tmW, const Params p)
 }
 
 int g_impl = 0;      // 0 = by M: streaming GEMV (gemm_w4a16_stream.cu; the older GEMV forms of gemm_w4a16_gemv.cu when K does not suit it)
-                     // for one token, the prefill kernel with the weights in tensor memory (gemm_w4a16_prefill_ts.cu) above 16
-                     // tokens, else the warp-MMA kernel (gemm_w4a16.cu); 5 = the streaming GEMV where it applies; 8 = that prefill
+                     // for one token, the prefill kernel with the weights in tensor memory (gemm_w4a16_prefill_ts.cu) from 64
+                     // tokens on (from 17 when N >= 8192), else the warp-MMA kernel (gemm_w4a16.cu); 5 = the streaming GEMV where it applies; 8 = that prefill
                      // kernel for every M; 6 / 7 = the prefill kernel that converts through shared memory (gemm_w4a16_prefill.cu;
                      // offset taken out by rows of ones / by the converters);
                      // 1 = tcgen05 kernel (this file); 2 = warp-MMA kernel for every M; 3 / 4 = GEMV up to 4 tokens, weights
@@ -385,7 +385,9 @@ extern "C" int b200q_gemm_w4a16(const void* X, const void* Wq, const void* S, vo
                                 void* stream)
 {
     using namespace b200q;
-    if (((M > 16 && w4tc::g_impl == 0) || w4tc::g_impl == 8) && group == 128 && K > 0 && K % 128 == 0)
+    // measured crossover against the warp-MMA kernel: from 64 tokens on, and from 17 where the weight rows alone
+    // fill the machine's tiles (N >= 8192)
+    if (((M > 16 && (M >= 64 || N >= 8192) && w4tc::g_impl == 0) || w4tc::g_impl == 8) && group == 128 && K > 0 && K % 128 == 0)
         return gemm_w4a16_prefill_ts(X, Wq, S, Y, M, N, K, group, stream);
     if ((w4tc::g_impl == 6 || w4tc::g_impl == 7) && group == 128 && K > 0 && K % 128 == 0 && K <= 16384)
         return gemm_w4a16_prefill(X, Wq, S, Y, M, N, K, group, w4tc::g_impl == 7 ? 1 : 0, stream);

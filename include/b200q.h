@@ -154,8 +154,8 @@ int b200q_nvfp4_set_tile_n(int bn);
 int b200q_nvfp4_set_2cta(int on);      /* NVFP4 GEMM on CTA pairs (256 x 192 / 256 x 256 tiles per pair) when M > 128 and the
                                         * tile width is not 128; default on */
 int b200q_w4a16_set_impl(int impl);     /* 0 = by M (default): streaming CUDA-core GEMV for one token (the older GEMV forms when K is not
-                                         * a multiple of 2048 or exceeds 16384), warp-MMA kernel for 2..16 tokens, above 16 the
-                                         * tcgen05 prefill kernel that keeps the converted weights in tensor memory (group-wise
+                                         * a multiple of 2048 or exceeds 16384), warp-MMA kernel for few tokens, from 64 tokens on (from
+                                         * 17 when N >= 8192: the measured crossover) the tcgen05 prefill kernel that keeps the converted weights in tensor memory (group-wise
                                          * partial-sum scaling, product computed transposed);
                                          * 5 / 8 = the streaming GEMV / that prefill kernel wherever they apply;
                                          * 6 / 7 = the prefill kernel that converts through shared memory (the integer offset taken

@@ -120,12 +120,12 @@ def test_prefill_form(shape, form, impl):
 
 def test_prefill_known_answer_and_default_dispatch(impl):
     """Coordinate-dependent S4 values (op/test/arch_primitives/ptx_mma_integer.cu:61-74) with scales 1 and 0.5 per
-    group: every product and sum is exact, so the output equals bf16(expected) bit for bit; 48 tokens go to the
+    group: every product and sum is exact, so the output equals bf16(expected) bit for bit; 80 tokens go to the
     prefill kernel by default."""
     import cudaop_b200 as ops
     if impl != (0, 0):
         pytest.skip("default dispatch only")
-    M, N, K = 48, 40, 256
+    M, N, K = 80, 40, 256
     W = np.array([[((n * 5 + k * 3 + 2) % 15) - 7 for k in range(K)] for n in range(N)], np.int8)
     X = np.array([[((m * 2 + k * 7 + 4) % 15) - 7 for k in range(K)] for m in range(M)], np.float32)
     s = np.full((N, K // 128), 1.0, np.float32); s[:, 1] = 0.5
